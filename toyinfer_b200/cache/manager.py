@@ -15,8 +15,9 @@ A group with a window keeps a ring of ``ring_rows`` >= window positions per sequ
 step points there and what it writes is never read.
 
 Fixed-size states live in one tensor per entry, [slots + 1, *shape], and are zeroed
-when a slot is handed out.  This architecture asks for none; the area exists so that a
-mixer with a state can be added without touching the cache.
+when a slot is handed out (a linear-attention mixer keeps its [heads, dim, vdim] state there).
+A request with ``values=False`` gets rows without a second array beside them (a latent that
+serves as key and value at once).
 
 The reference keeps one sequence's keys and values as [layers, max_seq_len, kv_dim]
 (src/transformer.cpp:188-195) and the position in a host variable
@@ -43,7 +44,7 @@ class KVView:
     """What a mixer's kernels need to reach one entry's keys and values."""
 
     k_pages: torch.Tensor          # [pages + 1, kv_heads, PAGE, head_dim]
-    v_pages: torch.Tensor
+    v_pages: Optional[torch.Tensor]   # None in a group that keeps one row per position only
     page_table: torch.Tensor       # [slots + 1, pages_per_seq] int32, on the device
     n_kv_heads: int
     head_dim: int
@@ -73,7 +74,7 @@ class _KVGroup:
         self.pool = PagePool(n_pages)
         shape = (len(entries), n_pages + 1, req.n_kv_heads, PAGE, req.head_dim)
         self.k = torch.zeros(shape, dtype=dtype, device=device)
-        self.v = torch.zeros(shape, dtype=dtype, device=device)
+        self.v = torch.zeros(shape, dtype=dtype, device=device) if req.values else None
         self.table_host = np.zeros((n_slots + 1, self.pages_per_seq), dtype=np.int32)
         self.table = torch.zeros((n_slots + 1, self.pages_per_seq), dtype=torch.int32, device=device)
         self.slot_pages: Dict[int, List[int]] = {}
@@ -112,15 +113,15 @@ class _KVGroup:
 
     def view(self, entry: int) -> KVView:
         i = self.entries.index(entry)
-        return KVView(self.k[i], self.v[i], self.table, self.req.n_kv_heads, self.req.head_dim,
-                      self.req.window, self.ring_rows)
+        return KVView(self.k[i], self.v[i] if self.v is not None else None, self.table, self.req.n_kv_heads,
+                      self.req.head_dim, self.req.window, self.ring_rows)
 
 
 def bytes_per_token(requests: Sequence[Any], dtype: torch.dtype) -> int:
     """Bytes of cache that one position of one sequence takes, over all schedule entries' requests
     (keys and values; fixed-size states do not grow with the length and count nothing here)."""
     elem = torch.empty((), dtype=dtype).element_size()
-    return sum(2 * r.n_kv_heads * r.head_dim * elem for r in requests if isinstance(r, KVRequest))
+    return sum((2 if r.values else 1) * r.n_kv_heads * r.head_dim * elem for r in requests if isinstance(r, KVRequest))
 
 
 class CacheManager:
@@ -211,7 +212,7 @@ class CacheManager:
     def bytes(self) -> int:
         n = 0
         for g in self.kv_groups:
-            n += 2 * g.k.numel() * g.k.element_size()
+            n += (2 if g.v is not None else 1) * g.k.numel() * g.k.element_size()
         for t in self.states.values():
             n += t.numel() * t.element_size()
         return n

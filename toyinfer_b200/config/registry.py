@@ -50,8 +50,10 @@ def resolve_architecture(name: str) -> Architecture:
 
 def architecture_of(raw: Dict[str, Any], source: str = "config") -> Architecture:
     archs = raw.get("architectures")
+    if archs is None and isinstance(raw.get("architecture"), str):       # some designs name themselves in one string
+        return resolve_architecture(raw["architecture"])
     if not isinstance(archs, list) or not archs or not isinstance(archs[0], str):
-        raise ConfigError(f"{source}: 'architectures' must be a non-empty list of strings")
+        raise ConfigError(f"{source}: 'architectures' must be a non-empty list of strings (or 'architecture' a string)")
     return resolve_architecture(archs[0])
 
 

@@ -1,0 +1,450 @@
+// Attention over a shared low-rank latent (multi-head latent attention), CUDA cores,
+// everything after the loads in 32-bit.
+//
+// Per token the cache keeps one row of W = rank + rot elements for all heads: the latent c
+// (RMS-normed down-projection) and one rotated key part r.  Head h's key is
+// [Wuk_h c | r] and its value Wuv_h c; with q_h = [a_h | b_h] (b_h rotated)
+//     s_hj = (a_h . Wuk_h c_j + b_h . r_j) * scale = ((Wuk_h^T a_h) . c_j + b_h . r_j) * scale
+//     o_h  = Wuv_h (sum_j p_hj c_j)
+// so the kernels here work on the cached rows themselves: the query is carried into the
+// latent space first (`absorb`), the attention runs as many query heads over ONE key/value
+// row per position (the value is the row's first `rank` elements), and the result is
+// carried out through Wuv (`expand`).  Keys and values per head are never formed.
+//
+// Softmax: position i sees j with 0 <= i - j < window (window <= 0: all j <= i); the
+// denominator also holds exp(sink_h) when sinks are given (a learned logit without key or
+// value, not scaled).
+//
+// Kernels:
+//   latent_prep    per token: c = rms(d[:rank]) * w, r = rotate(d[rank:]) at the token's
+//                  position, the row [c | r] to a dense step buffer and (optionally) to the
+//                  paged cache; the rotated part of every query head is rotated in place.
+//   latent_store   rows of the step buffer to the paged cache (for a ring whose rows the
+//                  step's own attention still had to read).
+//   latent_absorb  qa[m, h] = [Wuk_h^T a_{m,h} | b_{m,h}] in float32.
+//   latent_attn    the attention; a sequence's new tokens follow `seq_start[b]` positions in
+//                  the cache (rows below the start are read from pages, the others from the
+//                  step buffer), any mix of starts and counts in one launch.
+//   latent_expand  o[m, h] = Wuv_h ol[m, h].
+#include "common.cuh"
+
+namespace {
+
+struct LatentPages {
+    void* pages;                 // [n_pages, page_size, W]
+    const int* page_table; int table_width; int page_size; int ring_rows; int n_pages;
+};
+
+template <typename T>
+__device__ __forceinline__ void store_row_to_pages(const LatentPages& kv, int slot, int pos, int W, const T* row_vals,
+                                                   int tid, int nthreads) {
+    const int row = kv.ring_rows > 0 ? pos % kv.ring_rows : pos;
+    const int pidx = row / kv.page_size;
+    if (pidx >= kv.table_width) return;
+    const int page = kv.page_table[(size_t)slot * kv.table_width + pidx];
+    if (page < 0 || page >= kv.n_pages) return;
+    T* dst = (T*)kv.pages + ((size_t)page * kv.page_size + row % kv.page_size) * W;
+    for (int i = tid; i < W; i += nthreads) dst[i] = row_vals[i];
+}
+
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void latent_prep_kernel(const T* __restrict__ d, long long d_stride, T* __restrict__ q, long long q_stride,
+                                   int n_heads, int plain, int rank, int rot, const float* __restrict__ norm_w, float eps,
+                                   const float* __restrict__ cos_t, const float* __restrict__ sin_t, int max_pos,
+                                   const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
+                                   const int* __restrict__ seq_slot, T* __restrict__ lat, LatentPages kv) {
+    ti_pdl_trigger();
+    extern __shared__ float sm[];        // W floats, then W values of T, then 33
+    const int W = rank + rot;
+    float* vals = sm;
+    float* red = sm + W;
+    T* rounded = reinterpret_cast<T*>(red + 33);
+    ti_pdl_sync();
+    d = ti_dependent(d); q = ti_dependent(q);
+    const int m = blockIdx.x, t = threadIdx.x, nt = blockDim.x;
+    const int pos = min(max(tok_pos[m], 0), max_pos - 1);
+    const int half = rot >> 1;
+    const float* cs = cos_t + (size_t)pos * half;
+    const float* sn = sin_t + (size_t)pos * half;
+    const T* drow = d + (size_t)m * d_stride;
+    float ss = 0.f;
+    for (int i = t; i < W; i += nt) {
+        const float x = to_f32(drow[i]);
+        vals[i] = x;
+        if (i < rank) ss = fmaf(x, x, ss);
+    }
+    ss = block_sum(ss, red);             // (also makes vals visible)
+    const float inv = rsqrtf(ss / (float)rank + eps);
+    for (int i = t; i < rank; i += nt) rounded[i] = from_f32<T>(vals[i] * inv * norm_w[i]);
+    for (int i = t; i < half; i += nt) {
+        const float u = vals[rank + i], v = vals[rank + i + half], c = cs[i], s = sn[i];
+        rounded[rank + i] = from_f32<T>(u * c - v * s);
+        rounded[rank + i + half] = from_f32<T>(v * c + u * s);
+    }
+    __syncthreads();
+    if (lat)
+        for (int i = t; i < W; i += nt) lat[(size_t)m * W + i] = rounded[i];
+    if (kv.pages) store_row_to_pages<T>(kv, seq_slot[tok_seq[m]], tok_pos[m], W, rounded, t, nt);
+    // the rotated part of every query head, in place
+    if (q) {
+        const int hd = plain + rot;
+        for (int idx = t; idx < n_heads * half; idx += nt) {
+            const int h = idx / half, i = idx - h * half;
+            T* p = q + (size_t)m * q_stride + (size_t)h * hd + plain;
+            const float u = to_f32(p[i]), v = to_f32(p[i + half]), c = cs[i], s = sn[i];
+            p[i] = from_f32<T>(u * c - v * s);
+            p[i + half] = from_f32<T>(v * c + u * s);
+        }
+    }
+}
+
+template <typename T>
+__global__ void latent_store_kernel(const T* __restrict__ lat, int W, const int* __restrict__ tok_pos,
+                                    const int* __restrict__ tok_seq, const int* __restrict__ seq_slot, LatentPages kv) {
+    ti_pdl_trigger();
+    ti_pdl_sync();
+    lat = ti_dependent(lat);
+    const int m = blockIdx.x;
+    store_row_to_pages<T>(kv, seq_slot[tok_seq[m]], tok_pos[m], W, lat + (size_t)m * W, threadIdx.x, blockDim.x);
+}
+
+// ---------------------------------------------------------------------------
+// qa[m, h, 0:rank] = sum_d q[m, h, d] * uk[h, d, 0:rank];  qa[m, h, rank:] = q[m, h, plain:]
+// uk: [heads * plain, rank] (row (h, d)).  Grid (token tiles of TM, heads), 128 threads over the rank.
+constexpr int ABS_TM = 8, ABS_THREADS = 128, ABS_RPT = 8;      // rank up to 128 * 8
+
+template <typename T>
+__global__ void __launch_bounds__(ABS_THREADS)
+latent_absorb_kernel(const T* __restrict__ q, long long q_stride, const T* __restrict__ uk, float* __restrict__ qa,
+                     int M, int n_heads, int plain, int rank, int rot) {
+    ti_pdl_trigger();
+    extern __shared__ float qs[];        // [TM][plain]
+    ti_pdl_sync();
+    q = ti_dependent(q);
+    const int m0 = blockIdx.x * ABS_TM, h = blockIdx.y, t = threadIdx.x;
+    const int hd = plain + rot, W = rank + rot;
+    for (int idx = t; idx < ABS_TM * plain; idx += ABS_THREADS) {
+        const int mm = idx / plain, dd = idx - mm * plain;
+        qs[idx] = (m0 + mm < M) ? to_f32(q[(size_t)(m0 + mm) * q_stride + (size_t)h * hd + dd]) : 0.f;
+    }
+    for (int idx = t; idx < ABS_TM * rot; idx += ABS_THREADS) {
+        const int mm = idx / rot, dd = idx - mm * rot;
+        if (m0 + mm < M)
+            qa[((size_t)(m0 + mm) * n_heads + h) * W + rank + dd] = to_f32(q[(size_t)(m0 + mm) * q_stride + (size_t)h * hd + plain + dd]);
+    }
+    __syncthreads();
+    const T* ukh = uk + (size_t)h * plain * rank;
+    for (int r0 = 0; r0 < rank; r0 += ABS_THREADS * ABS_RPT) {
+        float acc[ABS_RPT][ABS_TM];
+#pragma unroll
+        for (int j = 0; j < ABS_RPT; j++)
+#pragma unroll
+            for (int mm = 0; mm < ABS_TM; mm++) acc[j][mm] = 0.f;
+        for (int dd = 0; dd < plain; dd++) {
+            float wv[ABS_RPT];
+#pragma unroll
+            for (int j = 0; j < ABS_RPT; j++) {
+                const int r = r0 + t + j * ABS_THREADS;
+                wv[j] = r < rank ? to_f32(ukh[(size_t)dd * rank + r]) : 0.f;
+            }
+#pragma unroll
+            for (int mm = 0; mm < ABS_TM; mm++) {
+                const float qv = qs[mm * plain + dd];
+#pragma unroll
+                for (int j = 0; j < ABS_RPT; j++) acc[j][mm] = fmaf(qv, wv[j], acc[j][mm]);
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < ABS_RPT; j++) {
+            const int r = r0 + t + j * ABS_THREADS;
+            if (r < rank)
+#pragma unroll
+                for (int mm = 0; mm < ABS_TM; mm++)
+                    if (m0 + mm < M) qa[((size_t)(m0 + mm) * n_heads + h) * W + r] = acc[j][mm];
+        }
+    }
+}
+
+// o[m, h, v] = sum_r uv[h, v, r] * ol[m, h, r].  uv: [heads * vdim, rank].  Grid (token tiles, heads);
+// a warp per output element row v, lanes along the rank.
+constexpr int EXP_TM = 8, EXP_THREADS = 128;
+
+template <typename T>
+__global__ void __launch_bounds__(EXP_THREADS)
+latent_expand_kernel(const float* __restrict__ ol, const T* __restrict__ uv, T* __restrict__ o, long long o_stride,
+                     int M, int n_heads, int vdim, int rank) {
+    ti_pdl_trigger();
+    extern __shared__ float os[];        // [TM][rank]
+    ti_pdl_sync();
+    ol = ti_dependent(ol);
+    const int m0 = blockIdx.x * EXP_TM, h = blockIdx.y, t = threadIdx.x;
+    for (int idx = t; idx < EXP_TM * rank; idx += EXP_THREADS) {
+        const int mm = idx / rank, r = idx - mm * rank;
+        os[idx] = (m0 + mm < M) ? ol[((size_t)(m0 + mm) * n_heads + h) * rank + r] : 0.f;
+    }
+    __syncthreads();
+    const int warp = t >> 5, lane = t & 31;
+    for (int v = warp; v < vdim; v += EXP_THREADS / 32) {
+        const T* wrow = uv + ((size_t)h * vdim + v) * rank;
+        float acc[EXP_TM];
+#pragma unroll
+        for (int mm = 0; mm < EXP_TM; mm++) acc[mm] = 0.f;
+        for (int r = lane; r < rank; r += 32) {
+            const float wv = to_f32(wrow[r]);
+#pragma unroll
+            for (int mm = 0; mm < EXP_TM; mm++) acc[mm] = fmaf(wv, os[mm * rank + r], acc[mm]);
+        }
+#pragma unroll
+        for (int mm = 0; mm < EXP_TM; mm++) {
+            const float s = warp_sum(acc[mm]);
+            if (lane == 0 && m0 + mm < M) o[(size_t)(m0 + mm) * o_stride + (size_t)h * vdim + v] = from_f32<T>(s);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// The attention.  A block works on 32 rows = QB consecutive queries of a sequence times HB heads
+// (HB * QB == 32) against key tiles of 32 positions; thread t works on row t / 4, its 4 threads split
+// a tile's keys (scores) and the latent's elements (output) between them.
+constexpr int LQ = 32, LK = 32, LTHREADS = 128;
+
+template <typename T, int MAXC>
+__global__ void __launch_bounds__(LTHREADS)
+latent_attn_kernel(const float* __restrict__ qa, const T* __restrict__ lat, float* __restrict__ ol,
+                   const int* __restrict__ cu_new, const int* __restrict__ seq_start, const int* __restrict__ seq_slot,
+                   int n_heads, int hb, int rank, int rot, float scale, int window, const float* __restrict__ sink,
+                   LatentPages kv) {
+    ti_pdl_trigger();
+    extern __shared__ float sm[];
+    ti_pdl_sync();
+    qa = ti_dependent(qa); lat = ti_dependent(lat);
+    const int W = rank + rot, ld = W + 1;
+    float* Qs = sm;                       // [LQ][ld]
+    float* Ks = Qs + LQ * ld;             // [LK][ld]
+    float* Ps = Ks + LK * ld;             // [LQ][LK + 1]
+    const int qb = LQ / hb;
+    const int b = blockIdx.z, h0 = blockIdx.y * hb, q0 = blockIdx.x * qb;
+    const int tok0 = cu_new[b];
+    const int n = cu_new[b + 1] - tok0;
+    if (q0 >= n) return;
+    const int start = seq_start[b], slot = seq_slot[b], end = start + n;
+    const int t = threadIdx.x, r = t >> 2, c4 = t & 3;
+    // row rr: query q0 + rr / hb, head h0 + rr % hb
+    for (int idx = t; idx < LQ * W; idx += LTHREADS) {
+        const int rr = idx / W, e = idx - rr * W;
+        const int qq = q0 + rr / hb, hh = h0 + rr % hb;
+        Qs[rr * ld + e] = (qq < n && hh < n_heads) ? qa[((size_t)(tok0 + qq) * n_heads + hh) * W + e] : 0.f;
+    }
+    const int my_q = q0 + r / hb, my_h = h0 + r % hb;
+    const bool row_ok = my_q < n && my_h < n_heads;
+    const int qi = start + my_q;
+    float acc[MAXC];
+#pragma unroll
+    for (int c = 0; c < MAXC; c++) acc[c] = 0.f;
+    // the sink stands in the denominator from the start: running maximum sink_h, running sum 1
+    float m_run = -INFINITY, l_run = 0.f;
+    if (sink && row_ok) { m_run = sink[my_h]; l_run = 1.f; }
+    const int nc = (rank + 3) >> 2;      // elements of the latent per thread (c4 + 4 c)
+    const int last_q = start + min(q0 + qb, n) - 1;
+    const int lo = window > 0 ? max(0, start + q0 - window + 1) : 0;
+    for (int k0 = (lo / LK) * LK; k0 <= last_q; k0 += LK) {
+        __syncthreads();
+        for (int idx = t; idx < LK * W; idx += LTHREADS) {
+            const int rr = idx / W, e = idx - rr * W;
+            const int p = k0 + rr;
+            float x = 0.f;
+            if (p >= start) {
+                if (p < end) x = to_f32(lat[(size_t)(tok0 + p - start) * W + e]);
+            } else if (p >= lo) {
+                const int row = kv.ring_rows > 0 ? p % kv.ring_rows : p;
+                const int pidx = row / kv.page_size;
+                const int page = pidx < kv.table_width ? kv.page_table[(size_t)slot * kv.table_width + pidx] : -1;
+                if (page >= 0 && page < kv.n_pages)
+                    x = to_f32(((const T*)kv.pages)[((size_t)page * kv.page_size + row % kv.page_size) * W + e]);
+            }
+            Ks[rr * ld + e] = x;
+        }
+        __syncthreads();
+        float s[8];
+#pragma unroll
+        for (int c = 0; c < 8; c++) s[c] = 0.f;
+        const float* qrow = Qs + r * ld;
+        for (int e = 0; e < W; e++) {
+            const float qv = qrow[e];
+#pragma unroll
+            for (int c = 0; c < 8; c++) s[c] = fmaf(qv, Ks[(c4 + 4 * c) * ld + e], s[c]);
+        }
+        float m_tile = -INFINITY;
+#pragma unroll
+        for (int c = 0; c < 8; c++) {
+            const int kj = k0 + c4 + 4 * c;
+            const bool ok = row_ok && kj <= qi && kj < end && (window <= 0 || kj > qi - window);
+            s[c] = ok ? s[c] * scale : -INFINITY;
+            m_tile = fmaxf(m_tile, s[c]);
+        }
+        m_tile = fmaxf(m_tile, __shfl_xor_sync(0xffffffffu, m_tile, 1));
+        m_tile = fmaxf(m_tile, __shfl_xor_sync(0xffffffffu, m_tile, 2));
+        const float m_new = fmaxf(m_run, m_tile);
+        float alpha = 1.f, l_tile = 0.f;
+        if (m_new > -INFINITY) {
+            alpha = expf(m_run - m_new);
+#pragma unroll
+            for (int c = 0; c < 8; c++) {
+                const float p = expf(s[c] - m_new);
+                Ps[r * (LK + 1) + c4 + 4 * c] = p;
+                l_tile += p;
+            }
+        } else {
+#pragma unroll
+            for (int c = 0; c < 8; c++) Ps[r * (LK + 1) + c4 + 4 * c] = 0.f;
+        }
+        l_tile += __shfl_xor_sync(0xffffffffu, l_tile, 1);
+        l_tile += __shfl_xor_sync(0xffffffffu, l_tile, 2);
+        l_run = l_run * alpha + l_tile;
+        m_run = m_new;
+        __syncwarp();
+#pragma unroll
+        for (int c = 0; c < MAXC; c++)
+            if (c < nc) acc[c] *= alpha;
+        const float* prow = Ps + r * (LK + 1);
+        for (int j = 0; j < LK; j++) {
+            const float p = prow[j];
+            const float* vrow = Ks + j * ld + c4;
+#pragma unroll
+            for (int c = 0; c < MAXC; c++)
+                if (c < nc) acc[c] = fmaf(p, vrow[4 * c], acc[c]);      // (an element past the rank is the rotated part: never stored)
+        }
+    }
+    if (row_ok) {
+        const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
+        float* orow = ol + ((size_t)(tok0 + my_q) * n_heads + my_h) * rank;
+#pragma unroll
+        for (int c = 0; c < MAXC; c++)
+            if (c < nc && c4 + 4 * c < rank) orow[c4 + 4 * c] = acc[c] * inv;
+    }
+}
+
+template <typename T, int MAXC>
+int launch_attn(const float* qa, const void* lat, float* ol, const int* cu_new, const int* seq_start, const int* seq_slot,
+                int n_seq, int max_new, int n_heads, int hb, int rank, int rot, float scale, int window, const float* sink,
+                const LatentPages& kv, cudaStream_t stream) {
+    const int W = rank + rot;
+    const size_t smem = ((size_t)(LQ + LK) * (W + 1) + (size_t)LQ * (LK + 1)) * sizeof(float);
+    TI_REQUIRE(smem <= 227 * 1024, "latent_attention: rows of %d elements need %zu bytes of shared memory", W, smem);
+    static size_t configured = 0;
+    if (smem > configured) {
+        TI_CUDA(cudaFuncSetAttribute(latent_attn_kernel<T, MAXC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        configured = smem;
+    }
+    const int qb = LQ / hb;
+    dim3 grid((max_new + qb - 1) / qb, (n_heads + hb - 1) / hb, n_seq);
+    TI_CUDA(ti_launch(latent_attn_kernel<T, MAXC>, grid, dim3(LTHREADS), smem, stream, qa, (const T*)lat, ol, cu_new, seq_start,
+                      seq_slot, n_heads, hb, rank, rot, scale, window, sink, kv));
+    TI_CHECK_LAUNCH("latent_attention");
+    return 0;
+}
+
+}  // namespace
+
+// d[M, rank + rot] (row stride d_stride) is the down-projection's output; q[M, heads, plain + rot] or null;
+// cos/sin: float32 [max_pos, rot / 2]; lat: [M, rank + rot] dense or null; pages null: no store.
+extern "C" int ti_latent_prep(const void* d, long long d_stride, void* q, long long q_stride, int n_heads, int plain,
+                              int rank, int rot, const float* norm_w, float eps, const float* cos_t, const float* sin_t,
+                              int max_pos, const int* tok_pos, const int* tok_seq, const int* seq_slot, void* lat,
+                              void* pages, const int* page_table, int table_width, int page_size, int ring_rows, int n_pages,
+                              int M, int dtype, cudaStream_t stream) {
+    if (M == 0) return 0;
+    TI_REQUIRE(M > 0 && rank > 0 && rot >= 0 && rot % 2 == 0 && plain >= 0, "latent_prep: bad sizes");
+    TI_REQUIRE(rot == 0 || (cos_t && sin_t && max_pos > 0), "latent_prep: a rotated part needs cos and sin tables");
+    TI_REQUIRE(!pages || (page_table && page_size > 0 && table_width > 0 && n_pages > 0 && ring_rows % page_size == 0),
+               "latent_prep: incomplete cache description");
+    LatentPages kv{pages, page_table, table_width, page_size, ring_rows, n_pages};
+    const int W = rank + rot;
+    return ti_dispatch_dtype(dtype, [&](auto t) -> int {
+        using T = decltype(t);
+        const size_t smem = (size_t)(W + 33) * sizeof(float) + (size_t)W * sizeof(T);
+        TI_REQUIRE(smem <= 48 * 1024, "latent_prep: rows of %d elements are too long", W);
+        TI_CUDA(ti_launch_class<2>(latent_prep_kernel<T>, dim3(M), dim3(128), smem, stream, (const T*)d, d_stride, (T*)q, q_stride,
+                                   n_heads, plain, rank, rot, norm_w, eps, cos_t, sin_t, max_pos, tok_pos, tok_seq, seq_slot,
+                                   (T*)lat, kv));
+        TI_CHECK_LAUNCH("latent_prep");
+        return 0;
+    });
+}
+
+extern "C" int ti_latent_store(const void* lat, int W, const int* tok_pos, const int* tok_seq, const int* seq_slot,
+                               void* pages, const int* page_table, int table_width, int page_size, int ring_rows, int n_pages,
+                               int M, int dtype, cudaStream_t stream) {
+    if (M == 0) return 0;
+    TI_REQUIRE(pages && page_table && page_size > 0 && table_width > 0 && n_pages > 0 && ring_rows % page_size == 0,
+               "latent_store: incomplete cache description");
+    LatentPages kv{pages, page_table, table_width, page_size, ring_rows, n_pages};
+    return ti_dispatch_dtype(dtype, [&](auto t) -> int {
+        using T = decltype(t);
+        TI_CUDA(ti_launch_class<2>(latent_store_kernel<T>, dim3(M), dim3(128), 0, stream, (const T*)lat, W, tok_pos, tok_seq,
+                                   seq_slot, kv));
+        TI_CHECK_LAUNCH("latent_store");
+        return 0;
+    });
+}
+
+extern "C" int ti_latent_absorb(const void* q, long long q_stride, const void* uk, float* qa, int M, int n_heads, int plain,
+                                int rank, int rot, int dtype, cudaStream_t stream) {
+    if (M == 0) return 0;
+    TI_REQUIRE(M > 0 && n_heads > 0 && n_heads <= 65535 && plain >= 0 && rank > 0 && rot >= 0, "latent_absorb: bad sizes");
+    const size_t smem = (size_t)ABS_TM * (plain > 0 ? plain : 1) * sizeof(float);
+    TI_REQUIRE(smem <= 48 * 1024, "latent_absorb: heads of %d unrotated elements are too long", plain);
+    return ti_dispatch_dtype(dtype, [&](auto t) -> int {
+        using T = decltype(t);
+        TI_CUDA(ti_launch(latent_absorb_kernel<T>, dim3((M + ABS_TM - 1) / ABS_TM, n_heads), dim3(ABS_THREADS), smem, stream,
+                          (const T*)q, q_stride, (const T*)uk, qa, M, n_heads, plain, rank, rot));
+        TI_CHECK_LAUNCH("latent_absorb");
+        return 0;
+    });
+}
+
+extern "C" int ti_latent_expand(const float* ol, const void* uv, void* o, long long o_stride, int M, int n_heads, int vdim,
+                                int rank, int dtype, cudaStream_t stream) {
+    if (M == 0) return 0;
+    TI_REQUIRE(M > 0 && n_heads > 0 && n_heads <= 65535 && vdim > 0 && rank > 0, "latent_expand: bad sizes");
+    const size_t smem = (size_t)EXP_TM * rank * sizeof(float);
+    TI_REQUIRE(smem <= 48 * 1024, "latent_expand: a latent of %d elements is too long", rank);
+    return ti_dispatch_dtype(dtype, [&](auto t) -> int {
+        using T = decltype(t);
+        TI_CUDA(ti_launch(latent_expand_kernel<T>, dim3((M + EXP_TM - 1) / EXP_TM, n_heads), dim3(EXP_THREADS), smem, stream, ol,
+                          (const T*)uv, (T*)o, o_stride, M, n_heads, vdim, rank));
+        TI_CHECK_LAUNCH("latent_expand");
+        return 0;
+    });
+}
+
+// qa: float32 [M, heads, rank + rot]; lat: the step's rows [M, rank + rot]; ol: float32 [M, heads, rank].
+// hb: heads per block, a power of two up to 32.  sink: float32 [heads] or null.
+extern "C" int ti_latent_attn(const float* qa, const void* lat, float* ol, const int* cu_new, const int* seq_start,
+                              const int* seq_slot, int n_seq, int max_new, int n_heads, int hb, int rank, int rot, float scale,
+                              int window, const float* sink, const void* pages, const int* page_table, int table_width,
+                              int page_size, int ring_rows, int n_pages, int dtype, cudaStream_t stream) {
+    if (n_seq == 0 || max_new == 0) return 0;
+    TI_REQUIRE(n_seq > 0 && max_new > 0 && n_heads > 0 && rank > 0 && rot >= 0, "latent_attention: bad sizes");
+    TI_REQUIRE(hb >= 1 && hb <= LQ && (hb & (hb - 1)) == 0, "latent_attention: %d heads per block (a power of two up to %d)", hb, LQ);
+    TI_REQUIRE(n_seq <= 65535, "latent_attention: too many sequences for one launch");
+    TI_REQUIRE(pages && page_table && page_size > 0 && table_width > 0 && n_pages > 0 && ring_rows % page_size == 0,
+               "latent_attention: incomplete cache description");
+    TI_REQUIRE(ring_rows == 0 || (window > 0 && ring_rows >= window),
+               "latent_attention: a ring of %d rows needs a window of at most as many positions (got %d)", ring_rows, window);
+    TI_REQUIRE(rank <= 1024, "latent_attention: a latent of %d elements is not supported (up to 1,024)", rank);
+    LatentPages kv{const_cast<void*>(pages), page_table, table_width, page_size, ring_rows, n_pages};
+    return ti_dispatch_dtype(dtype, [&](auto t) -> int {
+        using T = decltype(t);
+        if (rank <= 64)
+            return launch_attn<T, 16>(qa, lat, ol, cu_new, seq_start, seq_slot, n_seq, max_new, n_heads, hb, rank, rot, scale, window, sink, kv, stream);
+        if (rank <= 128)
+            return launch_attn<T, 32>(qa, lat, ol, cu_new, seq_start, seq_slot, n_seq, max_new, n_heads, hb, rank, rot, scale, window, sink, kv, stream);
+        if (rank <= 256)
+            return launch_attn<T, 64>(qa, lat, ol, cu_new, seq_start, seq_slot, n_seq, max_new, n_heads, hb, rank, rot, scale, window, sink, kv, stream);
+        if (rank <= 512)
+            return launch_attn<T, 128>(qa, lat, ol, cu_new, seq_start, seq_slot, n_seq, max_new, n_heads, hb, rank, rot, scale, window, sink, kv, stream);
+        return launch_attn<T, 256>(qa, lat, ol, cu_new, seq_start, seq_slot, n_seq, max_new, n_heads, hb, rank, rot, scale, window, sink, kv, stream);
+    });
+}

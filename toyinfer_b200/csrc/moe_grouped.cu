@@ -1,0 +1,256 @@
+// Mixture-of-experts feed-forward: tokens grouped by expert, one product kernel over all groups.
+//
+// A step has P = tokens * top (token, choice) pairs; pair p = m * top + j uses expert
+// e_p.  `moe_route_table` takes e_p from a table indexed by the token's id (a router
+// without arithmetic: table[id, j]), counts the pairs of every expert and writes them out
+// grouped by expert: perm[i] is the pair at place i, off[e] .. off[e + 1] the places of expert e.
+// The order inside a group is whatever the atomics gave; no result depends on it, since every
+// pair's rows are computed for themselves.
+//
+// `moe_grouped` is the product kernel, used twice:
+//   first product   rows of x gathered by pair (token perm[i] / top), expert e's gate and up
+//                   matrices, then the expert's activation, into y[i] (places, grouped)
+//   second product  rows y[i], expert e's down matrix, result scattered to z[perm[i]] (pairs in
+//                   the tokens' order), scaled by the pair's weight
+// Tiles of 32 places x 64 weight rows; a tile lies inside one expert's group (groups are
+// walked tile by tile: the grid has an upper bound of tiles, ceil(P / 32) + experts).
+// Arithmetic on the CUDA cores in 32-bit; operands of the engine's type.
+//
+// `moe_combine`: out[m] = sum_j z[m * top + j], summed in the order of j.
+//
+// The expert's activation (ACT_CLAMPED_SWISH): g' = min(g, limit), u' = clamp(u, -limit, limit),
+// y = g' * sigmoid(alpha * g') * (u' + 1).
+// `relu2` (the dense feed-forward's activation, x -> max(x, 0)^2) is here as well.
+#include "common.cuh"
+
+namespace {
+
+constexpr int RT_THREADS = 1024;
+
+__global__ void moe_route_table_kernel(const int* __restrict__ ids, const int* __restrict__ table, int vocab, int top,
+                                       int n_experts, int M, int* __restrict__ perm, int* __restrict__ off,
+                                       int* __restrict__ pair_expert) {
+    ti_pdl_trigger();
+    extern __shared__ int cnt[];         // [n_experts] counts, then [n_experts + 1] offsets, then [n_experts] cursors
+    int* offs = cnt + n_experts;
+    int* cur = offs + n_experts + 1;
+    ti_pdl_sync();
+    ids = ti_dependent(ids);
+    const int P = M * top;
+    for (int e = threadIdx.x; e < n_experts; e += blockDim.x) { cnt[e] = 0; cur[e] = 0; }
+    __syncthreads();
+    for (int p = threadIdx.x; p < P; p += blockDim.x) {
+        const int m = p / top, j = p - m * top;
+        int id = ids[m];
+        id = min(max(id, 0), vocab - 1);
+        int e = table[(size_t)id * top + j];
+        e = min(max(e, 0), n_experts - 1);
+        pair_expert[p] = e;
+        atomicAdd(&cnt[e], 1);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int a = 0;
+        for (int e = 0; e < n_experts; e++) { offs[e] = a; a += cnt[e]; }
+        offs[n_experts] = a;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e <= n_experts; e += blockDim.x) off[e] = offs[e];
+    for (int p = threadIdx.x; p < P; p += blockDim.x) {
+        const int e = pair_expert[p];
+        perm[offs[e] + atomicAdd(&cur[e], 1)] = p;
+    }
+}
+
+constexpr int GM = 32, GN = 64, GK = 32, G_THREADS = 256;
+
+enum { ACT_NONE = 0, ACT_CLAMPED_SWISH = 1 };
+
+// A: rows of `a` ([*, K], row stride lda); row of place i is a[(GATHER ? perm[i] / top : i)].
+// W: [n_experts, N, K] (and W2 of the same shape when PAIR: the up matrix beside the gate matrix).
+// out: PAIR -> y[i, n] = act(gate, up);  else z[(SCATTER ? perm[i] : i), n] = product * scale.
+template <typename T, bool PAIR>
+__global__ void __launch_bounds__(G_THREADS)
+moe_grouped_kernel(const T* __restrict__ a, long long lda, const T* __restrict__ W, const T* __restrict__ W2,
+                   T* __restrict__ out, long long ldo, const int* __restrict__ perm, const int* __restrict__ off,
+                   int n_experts, int N, int K, int top, int gather, int scatter, float scale, float limit, float alpha) {
+    ti_pdl_trigger();
+    __shared__ float As[GK][GM + 1];
+    __shared__ float Ws[GK][GN + 1];
+    __shared__ float W2s[PAIR ? GK : 1][GN + 1];
+    __shared__ int rows[GM];
+    __shared__ int where[3];             // expert, first place, places in the tile
+    ti_pdl_sync();
+    a = ti_dependent(a); perm = ti_dependent(perm); off = ti_dependent(off);
+    if (threadIdx.x == 0) {
+        // tile blockIdx.x of the walk over the groups
+        int t = blockIdx.x, e = 0, found = -1, first = 0, cnt = 0;
+        for (; e < n_experts; e++) {
+            const int lo = off[e], hi = off[e + 1];
+            const int tiles = (hi - lo + GM - 1) / GM;
+            if (t < tiles) { found = e; first = lo + t * GM; cnt = min(GM, hi - first); break; }
+            t -= tiles;
+        }
+        where[0] = found; where[1] = first; where[2] = cnt;
+    }
+    __syncthreads();
+    const int e = where[0], first = where[1], cnt = where[2];
+    if (e < 0) return;
+    const int n0 = blockIdx.y * GN;
+    if (threadIdx.x < GM) {
+        const int i = first + threadIdx.x;
+        int r = -1;
+        if (threadIdx.x < cnt) r = gather ? perm[i] / top : i;
+        rows[threadIdx.x] = r;
+    }
+    __syncthreads();
+    const T* We = W + (size_t)e * N * K;
+    const T* W2e = PAIR ? W2 + (size_t)e * N * K : nullptr;
+    // thread (ty, tx): places ty, ty + 8, ty + 16, ty + 24; weight rows tx, tx + 32
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    float acc[4][2], acc2[4][2];
+#pragma unroll
+    for (int i = 0; i < 4; i++)
+#pragma unroll
+        for (int j = 0; j < 2; j++) { acc[i][j] = 0.f; acc2[i][j] = 0.f; }
+    for (int k0 = 0; k0 < K; k0 += GK) {
+        for (int idx = threadIdx.x; idx < GM * GK; idx += G_THREADS) {
+            const int r = idx / GK, kk = idx - r * GK;
+            const int src = rows[r];
+            As[kk][r] = (src >= 0 && k0 + kk < K) ? to_f32(a[(size_t)src * lda + k0 + kk]) : 0.f;
+        }
+        for (int idx = threadIdx.x; idx < GN * GK; idx += G_THREADS) {
+            const int r = idx / GK, kk = idx - r * GK;
+            const bool ok = n0 + r < N && k0 + kk < K;
+            Ws[kk][r] = ok ? to_f32(We[(size_t)(n0 + r) * K + k0 + kk]) : 0.f;
+            if constexpr (PAIR) W2s[kk][r] = ok ? to_f32(W2e[(size_t)(n0 + r) * K + k0 + kk]) : 0.f;
+        }
+        __syncthreads();
+#pragma unroll 8
+        for (int kk = 0; kk < GK; kk++) {
+            float av[4], wv[2], w2v[2];
+#pragma unroll
+            for (int i = 0; i < 4; i++) av[i] = As[kk][ty + 8 * i];
+#pragma unroll
+            for (int j = 0; j < 2; j++) { wv[j] = Ws[kk][tx + 32 * j]; w2v[j] = PAIR ? W2s[kk][tx + 32 * j] : 0.f; }
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+#pragma unroll
+                for (int j = 0; j < 2; j++) {
+                    acc[i][j] = fmaf(av[i], wv[j], acc[i][j]);
+                    if constexpr (PAIR) acc2[i][j] = fmaf(av[i], w2v[j], acc2[i][j]);
+                }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const int r = ty + 8 * i;
+        if (r >= cnt) continue;
+        const int place = first + r;
+        const size_t orow = scatter ? (size_t)perm[place] : (size_t)place;
+#pragma unroll
+        for (int j = 0; j < 2; j++) {
+            const int n = n0 + tx + 32 * j;
+            if (n >= N) continue;
+            float y;
+            if constexpr (PAIR) {
+                // the two products are rounded to the engine's type first, as a kernel after the product would find them
+                const float g = fminf(to_f32(from_f32<T>(acc[i][j])), limit);
+                const float u = fminf(fmaxf(to_f32(from_f32<T>(acc2[i][j])), -limit), limit);
+                y = g * (1.0f / (1.0f + expf(-alpha * g))) * (u + 1.0f);
+            } else {
+                y = acc[i][j] * scale;
+            }
+            out[orow * ldo + n] = from_f32<T>(y);
+        }
+    }
+}
+
+template <typename T>
+__global__ void moe_combine_kernel(const T* __restrict__ z, T* __restrict__ out, int H, int top) {
+    ti_pdl_trigger();
+    ti_pdl_sync();
+    z = ti_dependent(z);
+    const size_t m = blockIdx.x;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float s = 0.f;
+        for (int j = 0; j < top; j++) s += to_f32(z[(m * top + j) * H + i]);
+        out[m * H + i] = from_f32<T>(s);
+    }
+}
+
+template <typename T>
+__global__ void relu2_kernel(const T* __restrict__ x, T* __restrict__ out, long long n) {
+    ti_pdl_trigger();
+    ti_pdl_sync();
+    x = ti_dependent(x);
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        const float v = fmaxf(to_f32(x[i]), 0.f);
+        out[i] = from_f32<T>(v * v);
+    }
+}
+
+}  // namespace
+
+// ids: int32 [M]; table: int32 [vocab, top]; perm: int32 [M * top]; off: int32 [n_experts + 1];
+// pair_expert: int32 scratch [M * top].
+extern "C" int ti_moe_route_table(const int* ids, const int* table, int vocab, int top, int n_experts, int M, int* perm,
+                                  int* off, int* pair_expert, cudaStream_t stream) {
+    if (M == 0) return 0;
+    TI_REQUIRE(M > 0 && top > 0 && n_experts > 0 && vocab > 0, "moe_route_table: bad sizes");
+    const size_t smem = (size_t)(3 * n_experts + 1) * sizeof(int);
+    TI_REQUIRE(smem <= 48 * 1024, "moe_route_table: %d experts are too many", n_experts);
+    TI_CUDA(ti_launch_class<1>(moe_route_table_kernel, dim3(1), dim3(RT_THREADS), smem, stream, ids, table, vocab, top, n_experts, M,
+                               perm, off, pair_expert));
+    TI_CHECK_LAUNCH("moe_route_table");
+    return 0;
+}
+
+// P places.  pair != 0: out[i, 0:N] = act(a_i W[e]^T, a_i W2[e]^T).  Else out[(scatter ? perm[i] : i)] = a_i W[e]^T * scale.
+extern "C" int ti_moe_grouped(const void* a, long long lda, const void* W, const void* W2, void* out, long long ldo,
+                              const int* perm, const int* off, int n_experts, int P, int N, int K, int top, int gather,
+                              int scatter, int pair, float scale, float limit, float alpha, int dtype, cudaStream_t stream) {
+    if (P == 0) return 0;
+    TI_REQUIRE(P > 0 && N > 0 && K > 0 && n_experts > 0 && top > 0, "moe_grouped: bad sizes");
+    TI_REQUIRE(!pair || W2, "moe_grouped: the paired form needs a second matrix");
+    const int tiles = (P + GM - 1) / GM + n_experts;
+    const int nblk = (N + GN - 1) / GN;
+    TI_REQUIRE(nblk <= 65535, "moe_grouped: %d weight rows are too many for one launch", N);
+    return ti_dispatch_dtype(dtype, [&](auto t) -> int {
+        using T = decltype(t);
+        if (pair)
+            TI_CUDA(ti_launch(moe_grouped_kernel<T, true>, dim3(tiles, nblk), dim3(G_THREADS), 0, stream, (const T*)a, lda,
+                              (const T*)W, (const T*)W2, (T*)out, ldo, perm, off, n_experts, N, K, top, gather, scatter, scale, limit, alpha));
+        else
+            TI_CUDA(ti_launch(moe_grouped_kernel<T, false>, dim3(tiles, nblk), dim3(G_THREADS), 0, stream, (const T*)a, lda,
+                              (const T*)W, (const T*)W2, (T*)out, ldo, perm, off, n_experts, N, K, top, gather, scatter, scale, limit, alpha));
+        TI_CHECK_LAUNCH("moe_grouped");
+        return 0;
+    });
+}
+
+extern "C" int ti_moe_combine(const void* z, void* out, int M, int H, int top, int dtype, cudaStream_t stream) {
+    if (M == 0) return 0;
+    TI_REQUIRE(M > 0 && H > 0 && top > 0, "moe_combine: bad sizes");
+    return ti_dispatch_dtype(dtype, [&](auto t) -> int {
+        using T = decltype(t);
+        TI_CUDA(ti_launch_class<1>(moe_combine_kernel<T>, dim3(M), dim3(H <= 256 ? 64 : 256), 0, stream, (const T*)z, (T*)out, H, top));
+        TI_CHECK_LAUNCH("moe_combine");
+        return 0;
+    });
+}
+
+extern "C" int ti_relu2(const void* x, void* out, long long n, int dtype, cudaStream_t stream) {
+    if (n == 0) return 0;
+    TI_REQUIRE(n > 0, "relu2: bad size");
+    return ti_dispatch_dtype(dtype, [&](auto t) -> int {
+        using T = decltype(t);
+        const int threads = 256;
+        const long long want = (n + threads - 1) / threads;
+        const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
+        TI_CUDA(ti_launch_class<1>(relu2_kernel<T>, dim3(blocks), dim3(threads), 0, stream, (const T*)x, (T*)out, n));
+        TI_CHECK_LAUNCH("relu2");
+        return 0;
+    });
+}

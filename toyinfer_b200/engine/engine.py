@@ -109,6 +109,10 @@ class Engine:
         limit = self.spec.max_positions
         self.max_seq_len = int(min(max_seq_len or limit, limit))
         self.max_tokens = int(max_tokens)
+        for pos in model.ctx.positions.values():       # tables built on demand get their length now, before any capture
+            ensure = getattr(pos, "ensure", None)
+            if ensure is not None:
+                ensure(self.max_seq_len)
         if n_slots is None:
             n_slots = max(self.max_batch, min(pages_for(self.max_tokens), 1024))
         self.cache = CacheManager(model.memory_requests(), self.max_tokens, n_slots, self.max_seq_len,

@@ -1,0 +1,108 @@
+"""Attention over a shared low-rank latent (csrc/attn_latent.cu): the rows that the cache keeps,
+the query carried into the latent space, the attention with a window and sinks, and the way out."""
+from __future__ import annotations
+
+from ctypes import c_float, c_int, c_longlong, c_void_p
+from typing import Optional
+
+import torch
+
+from . import KernelError, _call, _code, _need_cuda, _ptr, _stream
+from .wide import _fn
+
+P, I, L, F = c_void_p, c_int, c_longlong, c_float
+
+
+def _pages(mem):
+    if mem is None:
+        return (None, None, 0, 0, 0, 0)
+    pt = mem.page_table
+    return (_ptr(mem.k_pages), _ptr(pt), pt.shape[1], mem.page_size, mem.ring_rows, mem.k_pages.shape[0])
+
+
+def _check_mem(mem, W: int, dtype, what: str) -> None:
+    if mem.n_kv_heads != 1 or mem.head_dim != W or mem.k_pages.dtype != dtype or not mem.k_pages.is_contiguous():
+        raise KernelError(f"{what}: the cache does not hold rows of {W} {dtype} elements")
+
+
+def prep(d: torch.Tensor, q: Optional[torch.Tensor], rank: int, rot: int, norm_w: torch.Tensor, eps: float, tables,
+         batch, mem=None) -> torch.Tensor:
+    """d[M, rank + rot] (dense rows, any row stride): returns the step's rows [norm(d[:rank]) | rotate(d[rank:])],
+    stores them to ``mem``'s pages when given, and rotates q[M, heads, plain + rot]'s rotated part in place."""
+    _need_cuda(d, q, norm_w, what="latent_prep")
+    M, W = d.shape
+    if W != rank + rot or d.stride(1) != 1:
+        raise KernelError("latent_prep: the down-projection's rows do not fit rank + rot")
+    if norm_w.dtype != torch.float32 or norm_w.shape != (rank,) or not norm_w.is_contiguous():
+        raise KernelError("latent_prep: the norm weight must be float32 [rank]")
+    cos = sin = None
+    max_pos = 0
+    if rot:
+        cos, sin, dim = tables
+        if dim != rot or cos.dtype != torch.float32 or cos.shape != sin.shape or cos.shape[1] * 2 != rot:
+            raise KernelError("latent_prep: rotary tables must be float32 [positions, rot / 2]")
+        max_pos = cos.shape[0]
+        if batch.max_pos_after > max_pos:
+            raise KernelError(f"latent_prep: position {batch.max_pos_after - 1} is beyond the rotary tables' {max_pos}")
+    nh = plain = 0
+    qs = 0
+    if q is not None:
+        if q.dim() != 3 or q.shape[0] != M or q.stride(2) != 1 or q.stride(1) != q.shape[2] or q.dtype != d.dtype:
+            raise KernelError("latent_prep: q must be [M, heads, plain + rot] with dense heads")
+        nh, plain, qs = q.shape[1], q.shape[2] - rot, q.stride(0)
+    if mem is not None:
+        _check_mem(mem, W, d.dtype, "latent_prep")
+    lat = torch.empty((M, W), dtype=d.dtype, device=d.device)
+    _call(_fn("ti_latent_prep", [P, L, P, L, I, I, I, I, P, F, P, P, I, P, P, P, P, P, P, I, I, I, I, I, I, P]),
+          _ptr(d), d.stride(0), _ptr(q), qs, nh, plain, rank, rot, _ptr(norm_w), float(eps), _ptr(cos), _ptr(sin), max_pos,
+          _ptr(batch.tok_pos), _ptr(batch.tok_seq), _ptr(batch.seq_slot), _ptr(lat), *_pages(mem), M, _code(d, "latent_prep"),
+          _stream())
+    return lat
+
+
+def store(lat: torch.Tensor, batch, mem) -> None:
+    """The step's rows to the cache."""
+    M, W = lat.shape
+    _check_mem(mem, W, lat.dtype, "latent_store")
+    _call(_fn("ti_latent_store", [P, I, P, P, P, P, P, I, I, I, I, I, I, P]), _ptr(lat), W, _ptr(batch.tok_pos),
+          _ptr(batch.tok_seq), _ptr(batch.seq_slot), *_pages(mem), M, _code(lat, "latent_store"), _stream())
+
+
+def heads_per_block(n_heads: int, one_token_each: bool) -> int:
+    """Heads that share a block's key tiles: as many as fit its 32 rows when every sequence brings one query, else 8
+    (4 consecutive queries read nearly the same keys)."""
+    cap = 32 if one_token_each else 8
+    hb = 1
+    while hb < min(n_heads, cap):
+        hb <<= 1
+    return hb
+
+
+def attention(q: torch.Tensor, lat: torch.Tensor, uk: torch.Tensor, uv: torch.Tensor, vdim: int, rank: int, rot: int,
+              scale: float, window: int, sink: Optional[torch.Tensor], batch, mem) -> torch.Tensor:
+    """q[M, heads, plain + rot] (rotated part already rotated), the step's rows lat[M, rank + rot], uk[heads * plain, rank],
+    uv[heads * vdim, rank] -> [M, heads * vdim].  Keys at positions below a sequence's start come from ``mem``."""
+    _need_cuda(q, lat, uk, uv, sink, what="latent_attention")
+    M, nh, hd = q.shape
+    plain, W = hd - rot, rank + rot
+    if lat.shape != (M, W) or not lat.is_contiguous() or lat.dtype != q.dtype:
+        raise KernelError("latent_attention: the step's rows do not fit the queries")
+    if uk.shape != (nh * plain, rank) or uv.shape != (nh * vdim, rank) or not uk.is_contiguous() or not uv.is_contiguous() \
+            or uk.dtype != q.dtype or uv.dtype != q.dtype:
+        raise KernelError("latent_attention: the up-projections do not fit")
+    if sink is not None and (sink.dtype != torch.float32 or sink.shape != (nh,) or not sink.is_contiguous()):
+        raise KernelError("latent_attention: sinks must be float32 [heads]")
+    _check_mem(mem, W, q.dtype, "latent_attention")
+    code = _code(q, "latent_attention")
+    qa = torch.empty((M, nh, W), dtype=torch.float32, device=q.device)
+    _call(_fn("ti_latent_absorb", [P, L, P, P, I, I, I, I, I, I, P]), _ptr(q), q.stride(0), _ptr(uk), _ptr(qa), M, nh, plain,
+          rank, rot, code, _stream())
+    ol = torch.empty((M, nh, rank), dtype=torch.float32, device=q.device)
+    hb = heads_per_block(nh, batch.mode == "extend")
+    _call(_fn("ti_latent_attn", [P, P, P, P, P, P, I, I, I, I, I, I, F, I, P, P, P, I, I, I, I, I, P]),
+          _ptr(qa), _ptr(lat), _ptr(ol), _ptr(batch.cu_new), _ptr(batch.seq_start), _ptr(batch.seq_slot), batch.n_seq,
+          batch.max_new, nh, hb, rank, rot, float(scale), int(window), _ptr(sink), *_pages(mem), code, _stream())
+    o = torch.empty((M, nh * vdim), dtype=q.dtype, device=q.device)
+    _call(_fn("ti_latent_expand", [P, P, P, L, I, I, I, I, I, P]), _ptr(ol), _ptr(uv), _ptr(o), o.stride(0), M, nh, vdim, rank,
+          code, _stream())
+    return o

@@ -18,7 +18,7 @@ from .base import (
     registered_parts,
     unregister_part,
 )
-from . import norms, rope, attention, mlp, block, ends  # noqa: F401  (registration)
+from . import norms, rope, attention, latent_attention, lightning, mlp, block, parallel_block, ends  # noqa: F401  (registration)
 from .model import DecoderModel, LayerSpec, ModelSpec, ScheduleEntry
 
 __all__ = [

@@ -61,13 +61,15 @@ class ParamSpec:
 
     role: "matrix" (follows the engine's dtype), "norm" (follows the engine's
     dtype, but a tensor stored in 32-bit stays 32-bit), "int_table" (int32).
-    init: "normal" N(0, std), "one_plus_normal" 1 + N(0, std), "zeros", "ones".
+    init: "normal" N(0, std), "one_plus_normal" 1 + N(0, std), "zeros", "ones"; for an integer table
+    "distinct_below": every row holds different integers drawn from 0 .. high - 1.
     """
 
     shape: Tuple[int, ...]
     role: str = "matrix"
     init: str = "normal"
     std: float = 0.02
+    high: int = 0
 
 
 @dataclass(frozen=True)
@@ -118,6 +120,7 @@ class KVRequest:
     n_kv_heads: int
     head_dim: int
     window: int = 0
+    values: bool = True        # False: one row per position and kv head only (a mixer that reads its values out of the same row)
 
 
 @dataclass(frozen=True)
@@ -139,6 +142,11 @@ class Norm(Part):
         """As add_forward, but may leave the work to the reader's first product: a
         kernels.PendingNorm instead of a tensor (only for readers that say takes_pending_norm)."""
         return self.add_forward(h, delta)
+
+    def gather_add_forward(self, h: torch.Tensor, delta, rows: torch.Tensor) -> torch.Tensor:
+        """The norm of the rows ``rows`` of h + delta; h itself stays as it is."""
+        from .. import kernels as K
+        return self.forward(K.gather_add(h, delta, rows))
 
 
 class PositionEncoding(Part):

@@ -17,14 +17,16 @@ from typing import Dict, Optional
 import torch
 
 from .. import kernels as K
+from ..kernels import wide
 from .base import BuildContext, Embedding, Head, ParamSpec, PartSpec, build_part, register_part
 
 
 class TokenEmbedding(Embedding):
     def __init__(self, ctx: BuildContext, prefix: str, vocab_size: int, scale: float = 1.0,
-                 name: str = "model.embed_tokens.weight"):
+                 name: str = "model.embed_tokens.weight", wide: bool = False):
         self.vocab_size, self.hidden = int(vocab_size), ctx.hidden_size
         self.scale = float(scale)
+        self.wide = bool(wide)          # the rows come out as a float32 stream whatever the table's type
         self.name = prefix + name
         self.weight: Optional[torch.Tensor] = None
 
@@ -38,6 +40,12 @@ class TokenEmbedding(Embedding):
         return self.weight
 
     def forward(self, token_ids: torch.Tensor) -> torch.Tensor:
+        if self.wide:
+            return wide.embed_wide(self.weight, token_ids, self.scale)
+        return K.embed(self.weight, token_ids, self.scale)
+
+    def rows(self, token_ids: torch.Tensor) -> torch.Tensor:
+        """The table's rows in the table's own type (what a later layer adds to the stream once more)."""
         return K.embed(self.weight, token_ids, self.scale)
 
 
@@ -75,9 +83,12 @@ class LinearHead(Head):
         self.weight = self.ctx.embedding.table() if self.tied else tensors.pop(self.name)
 
     def forward(self, h: torch.Tensor, delta: Optional[torch.Tensor], rows: torch.Tensor) -> torch.Tensor:
-        x = K.gather_add(h, delta, rows)
         if self.norm is not None:
-            x = self.norm.forward(x)
+            x = self.norm.gather_add_forward(h, delta, rows)
+        elif h.dtype == torch.float32 and self.weight.dtype != torch.float32 or isinstance(delta, tuple):
+            x = wide.add_norm_wide(h, delta, None, 0.0, self.weight.dtype, rows=rows)
+        else:
+            x = K.gather_add(h, delta, rows)
         logits = K.linear(x, self.weight, out_dtype=torch.float32)
         if self.scale != 1.0 or self.softcap > 0.0:
             K.logit_scale_cap(logits, self.scale, self.softcap)

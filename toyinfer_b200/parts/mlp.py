@@ -50,3 +50,83 @@ class SwiGLU(FeedForward):
 
 
 register_part("feed_forward", "swiglu", SwiGLU)
+
+
+class SquaredReLU(FeedForward):
+    """y = Wdown relu(Wup x)^2; no gate, no bias."""
+
+    captures_start = True
+
+    def __init__(self, ctx: BuildContext, prefix: str, intermediate_size: int, names: Optional[Dict[str, str]] = None):
+        self.hidden = ctx.hidden_size
+        self.inter = int(intermediate_size)
+        n = {"up": "up", "down": "down"}
+        n.update(names or {})
+        self.names = {k: prefix + v for k, v in n.items()}
+        self.w_up = self.w_down = None
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        return {self.names["up"]: ParamSpec((self.inter, self.hidden)),
+                self.names["down"]: ParamSpec((self.hidden, self.inter))}
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        self.w_up = tensors.pop(self.names["up"]).contiguous()
+        self.w_down = tensors.pop(self.names["down"]).contiguous()
+
+    def forward(self, x, batch) -> torch.Tensor:
+        from ..kernels import moe as KM
+        return K.linear(KM.relu2(K.linear(x, self.w_up)), self.w_down)
+
+
+class TableMoE(FeedForward):
+    """Mixture of experts whose router is a table: token id t uses the experts table[t, 0..top-1] (all different),
+    each with weight 1/top.  An expert: g = min(Wgate x, limit), u = clamp(Wup x, -limit, limit),
+    y = Wdown (g * sigmoid(alpha * g) * (u + 1)); no biases.  The step's tokens are grouped by expert on the
+    device and every product runs once over all groups (kernels/moe.py)."""
+
+    captures_start = True
+
+    def __init__(self, ctx: BuildContext, prefix: str, n_experts: int, top: int, intermediate_size: int, limit: float,
+                 vocab_size: int, alpha: float = 1.702, names: Optional[Dict[str, str]] = None):
+        self.hidden = ctx.hidden_size
+        self.n_experts, self.top, self.inter = int(n_experts), int(top), int(intermediate_size)
+        self.limit, self.alpha, self.vocab = float(limit), float(alpha), int(vocab_size)
+        if not (1 <= self.top <= self.n_experts):
+            raise ValueError(f"moe at {prefix!r}: {self.top} of {self.n_experts} experts per token")
+        n = {"expert": "e{}.", "gate": "gate", "up": "up", "down": "down", "table": "table"}
+        n.update(names or {})
+        self.prefix, self.n = prefix, n
+        self.w_gate = self.w_up = self.w_down = self.table = None
+
+    def _name(self, e: int, which: str) -> str:
+        return self.prefix + self.n["expert"].format(e) + self.n[which]
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        s: Dict[str, ParamSpec] = {}
+        for e in range(self.n_experts):
+            s[self._name(e, "gate")] = ParamSpec((self.inter, self.hidden), std=0.05)
+            s[self._name(e, "up")] = ParamSpec((self.inter, self.hidden), std=0.05)
+            s[self._name(e, "down")] = ParamSpec((self.hidden, self.inter))
+        s[self.prefix + self.n["table"]] = ParamSpec((self.vocab, self.top), role="int_table", init="distinct_below",
+                                                     high=self.n_experts)
+        return s
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        E = range(self.n_experts)
+        self.w_gate = torch.stack([tensors.pop(self._name(e, "gate")) for e in E]).contiguous()
+        self.w_up = torch.stack([tensors.pop(self._name(e, "up")) for e in E]).contiguous()
+        self.w_down = torch.stack([tensors.pop(self._name(e, "down")) for e in E]).contiguous()
+        self.table = tensors.pop(self.prefix + self.n["table"]).to(torch.int32).contiguous()
+
+    def forward(self, x, batch) -> torch.Tensor:
+        from ..kernels import moe as KM
+        if batch is None:
+            raise RuntimeError("a table-routed feed-forward needs the step's token ids")
+        ids = batch.token_ids[: x.shape[0]]
+        perm, off = KM.route_by_table(ids, self.table, self.n_experts)
+        return KM.experts_ffn(x, perm, off, self.w_gate, self.w_up, self.w_down, self.top, self.limit, self.alpha,
+                              1.0 / self.top)
+
+
+register_part("feed_forward", "relu2", SquaredReLU)
+register_part("feed_forward", "table_moe", TableMoE)

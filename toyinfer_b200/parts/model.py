@@ -23,6 +23,7 @@ from typing import Any, Dict, List, Optional, Sequence, Tuple
 import torch
 
 from .. import kernels as K
+from ..kernels.wide import pending_terms
 from ..tracing import ranged
 from .base import BuildContext, ParamSpec, Part, PartSpec, build_part
 
@@ -37,6 +38,7 @@ class LayerSpec:
 class ScheduleEntry:
     layer: int                       # index into ModelSpec.layers
     memory_of: Optional[int] = None  # index of an earlier entry whose memory this one reads
+    add_embedding: bool = False      # the embedding's rows are added to the hidden state once more before this entry
 
 
 @dataclass
@@ -153,8 +155,18 @@ class DecoderModel(Part):
         for o, last in last_use.items():
             if last != o:
                 shared[o]["deferred"] = []     # writes to the memory that must wait for its last reader
+        again = None
+        if any(e.add_embedding for e in self.schedule):
+            rows = getattr(self.embedding, "rows", None)
+            again = rows(batch.token_ids) if rows is not None else self.embedding.forward(batch.token_ids)
         for i, e in enumerate(self.schedule):
             owner = owners[i]
+            if e.add_embedding:
+                # one more pending term: the norm that forms the sum takes it last
+                d0, d1, d2 = pending_terms(delta)
+                if d2 is not None:
+                    raise ValueError(f"schedule entry {i}: the pending sum has no room for the embedding's rows")
+                delta = (d0, d1, again)
             h, delta = self.blocks[e.layer].forward(h, delta, batch, memories[owner], shared[owner])
             if last_use[owner] == i:
                 for fn in shared[owner].get("deferred", ()):

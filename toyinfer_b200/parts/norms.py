@@ -14,15 +14,21 @@ from typing import Dict, Optional
 import torch
 
 from .. import kernels as K
+from ..kernels import wide
 from .base import BuildContext, Norm, ParamSpec, register_part
 
 
 class RMSNorm(Norm):
-    def __init__(self, ctx: BuildContext, prefix: str, size: int, eps: float, name: str = "weight"):
+    """``wide``: the hidden state it reads is a float32 stream whatever the engine's type, and what is pending on
+    it may be up to three terms (kernels/wide.py); the normed rows come out in the engine's type."""
+
+    def __init__(self, ctx: BuildContext, prefix: str, size: int, eps: float, name: str = "weight", wide: bool = False):
         self.size = int(size)
         self.eps = float(eps)
         self.weight_name = prefix + name
         self.weight: Optional[torch.Tensor] = None
+        self.wide = bool(wide)
+        self.out_dtype = ctx.dtype
 
     def param_specs(self) -> Dict[str, ParamSpec]:
         return {self.weight_name: ParamSpec((self.size,), role="norm", init="one_plus_normal")}
@@ -31,16 +37,29 @@ class RMSNorm(Norm):
         self.weight = tensors[self.weight_name]
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if self.wide:
+            return wide.add_norm_wide(x, None, self.weight, self.eps, self.out_dtype)
         return K.rmsnorm(x, self.weight, self.eps)
 
-    def add_forward(self, h: torch.Tensor, delta: Optional[torch.Tensor]) -> torch.Tensor:
+    def add_forward(self, h: torch.Tensor, delta) -> torch.Tensor:
+        if self.wide:
+            return wide.add_norm_wide(h, delta, self.weight, self.eps, self.out_dtype)
+        if isinstance(delta, tuple):
+            raise ValueError("a pending sum of several terms needs a norm over a float32 stream (wide=True)")
         if delta is None:
             return K.rmsnorm(h, self.weight, self.eps)
         return K.add_rmsnorm(h, delta, self.weight, self.eps)
 
-    def add_pending(self, h: torch.Tensor, delta: Optional[torch.Tensor]):
+    def add_pending(self, h: torch.Tensor, delta):
+        if self.wide:
+            return self.add_forward(h, delta)
         pending = K.pending_norm(h, delta, self.weight, self.eps)
         return pending if pending is not None else self.add_forward(h, delta)
+
+    def gather_add_forward(self, h: torch.Tensor, delta, rows: torch.Tensor) -> torch.Tensor:
+        if self.wide:
+            return wide.add_norm_wide(h, delta, self.weight, self.eps, self.out_dtype, rows=rows)
+        return super().gather_add_forward(h, delta, rows)
 
 
 register_part("norm", "rmsnorm", RMSNorm)

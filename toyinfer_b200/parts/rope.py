@@ -11,6 +11,7 @@ position has one angle whichever way the tokens are cut into steps.
 """
 from __future__ import annotations
 
+import math
 from typing import Optional, Tuple
 
 import torch
@@ -18,28 +19,78 @@ import torch
 from .base import BuildContext, PositionEncoding, register_part
 
 
-def rotary_tables(dim: int, theta: float, max_positions: int) -> Tuple[torch.Tensor, torch.Tensor]:
-    """cos and sin of pos * theta^(-2i/dim), computed in 64-bit, returned as float32."""
+def blended_frequencies(dim: int, theta: float, factor: float, original: int, fast: float, slow: float):
+    """Frequencies stretched for contexts longer than ``original`` positions ("YaRN": Peng, Quesnelle, Fan,
+    Shippole, 2023): pair i keeps theta^(-2i/dim) where its wave turns more than ``fast`` times over
+    ``original`` positions, is divided by ``factor`` where it turns fewer than ``slow`` times, and is blended
+    linearly in i between the two pair indices where that happens.  Returns (float64 frequencies, the magnitude
+    0.1 ln(factor) + 1 that cos and sin are multiplied by)."""
     half = dim // 2
     i = torch.arange(half, dtype=torch.float64)
-    inv_freq = torch.pow(torch.tensor(float(theta), dtype=torch.float64), -(2.0 * i) / dim)
+    base = torch.pow(torch.tensor(float(theta), dtype=torch.float64), -(2.0 * i) / dim)
+
+    def pair_index(turns: float) -> float:
+        return dim * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(theta))
+
+    lo = max(math.floor(pair_index(fast)), 0)
+    hi = min(math.ceil(pair_index(slow)), dim - 1)
+    ramp = torch.clamp((i - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+    return base / factor * ramp + base * (1.0 - ramp), 0.1 * math.log(factor) + 1.0
+
+
+def rotary_tables(dim: int, theta: float, max_positions: int, scaling: Optional[dict] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """cos and sin of pos * f_i with f_i = theta^(-2i/dim) (or the blended frequencies and magnitude of ``scaling``:
+    factor, original, fast, slow), computed in 64-bit, returned as float32."""
+    half = dim // 2
+    if scaling:
+        inv_freq, magnitude = blended_frequencies(dim, float(theta), float(scaling["factor"]), int(scaling["original"]),
+                                                  float(scaling["fast"]), float(scaling["slow"]))
+    else:
+        i = torch.arange(half, dtype=torch.float64)
+        inv_freq, magnitude = torch.pow(torch.tensor(float(theta), dtype=torch.float64), -(2.0 * i) / dim), 1.0
     pos = torch.arange(max_positions, dtype=torch.float64)
     ang = pos[:, None] * inv_freq[None, :]
-    return torch.cos(ang).to(torch.float32), torch.sin(ang).to(torch.float32)
+    return (torch.cos(ang) * magnitude).to(torch.float32), (torch.sin(ang) * magnitude).to(torch.float32)
 
 
 class RotaryHalf(PositionEncoding):
-    def __init__(self, ctx: BuildContext, prefix: str, dim: int, theta: float, max_positions: int):
+    """``scaling``: None, or the stretch for long contexts (see blended_frequencies).  ``max_positions`` is the
+    most the tables may ever hold; with ``lazy`` they are built for as many positions as ``ensure`` is told (the
+    engine says how long its sequences get before the first step), not for the model's nominal limit."""
+
+    def __init__(self, ctx: BuildContext, prefix: str, dim: int, theta: float, max_positions: int,
+                 scaling: Optional[dict] = None, lazy: bool = False):
         if dim % 2:
             raise ValueError(f"rotary dimension must be even, got {dim}")
         self.dim = int(dim)
         self.theta = float(theta)
         self.max_positions = int(max_positions)
-        cos, sin = rotary_tables(self.dim, self.theta, self.max_positions)
-        self.cos = cos.to(ctx.device).contiguous()
-        self.sin = sin.to(ctx.device).contiguous()
+        self.scaling = dict(scaling) if scaling else None
+        if self.scaling:
+            for key in ("factor", "original", "fast", "slow"):
+                if key not in self.scaling:
+                    raise ValueError(f"rotary scaling needs {key!r}")
+            if not (self.scaling["factor"] >= 1.0 and self.scaling["original"] > 0
+                    and self.scaling["fast"] > 0 and self.scaling["slow"] > 0):
+                raise ValueError(f"rotary scaling out of range: {self.scaling}")
+        self.device = ctx.device
+        self.cos = self.sin = None
+        if not lazy:
+            self.ensure(self.max_positions)
+
+    def ensure(self, n_positions: int) -> None:
+        """Tables for at least ``n_positions`` positions (never more than ``max_positions``).  Called before steps
+        are captured: a captured step keeps the tables' addresses."""
+        n = min(int(n_positions), self.max_positions)
+        if self.cos is not None and self.cos.shape[0] >= n:
+            return
+        cos, sin = rotary_tables(self.dim, self.theta, n, self.scaling)
+        self.cos = cos.to(self.device).contiguous()
+        self.sin = sin.to(self.device).contiguous()
 
     def rotary_tables(self) -> Optional[Tuple[torch.Tensor, torch.Tensor, int]]:
+        if self.cos is None:
+            self.ensure(min(self.max_positions, 4096))
         return self.cos, self.sin, self.dim
 
 

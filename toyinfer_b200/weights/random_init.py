@@ -30,6 +30,12 @@ def draw(spec: ParamSpec, name: str, seed: int, device="cpu") -> torch.Tensor:
     g = torch.Generator(device=device)
     g.manual_seed(_tensor_seed(seed, name))
     if spec.role == "int_table":
+        if spec.init == "distinct_below":
+            rows, width = spec.shape
+            if width > spec.high:
+                raise ValueError(f"{name}: {width} different integers below {spec.high} do not exist")
+            order = torch.rand((rows, spec.high), generator=g, device=device).argsort(dim=1)
+            return order[:, :width].to(torch.int32).contiguous()
         return torch.zeros(spec.shape, dtype=torch.int32, device=device)
     if spec.init == "zeros":
         return torch.zeros(spec.shape, dtype=torch.float32, device=device)
