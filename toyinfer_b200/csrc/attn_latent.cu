@@ -33,11 +33,15 @@ namespace {
 struct LatentPages {
     void* pages;                 // [n_pages, page_size, W]
     const int* page_table; int table_width; int page_size; int ring_rows; int n_pages;
+    const int* seq_len;          // each sequence's length after the step (for stores into a ring)
 };
 
 template <typename T>
-__device__ __forceinline__ void store_row_to_pages(const LatentPages& kv, int slot, int pos, int W, const T* row_vals,
+__device__ __forceinline__ void store_row_to_pages(const LatentPages& kv, int slot, int seq, int pos, int W, const T* row_vals,
                                                    int tid, int nthreads) {
+    // in a ring only the last ring_rows positions of the sequence are kept: an older row of this step
+    // must not land on the place of a newer one, whichever block runs last
+    if (kv.ring_rows > 0 && pos + kv.ring_rows < kv.seq_len[seq]) return;
     const int row = kv.ring_rows > 0 ? pos % kv.ring_rows : pos;
     const int pidx = row / kv.page_size;
     if (pidx >= kv.table_width) return;
@@ -85,7 +89,7 @@ __global__ void latent_prep_kernel(const T* __restrict__ d, long long d_stride, 
     __syncthreads();
     if (lat)
         for (int i = t; i < W; i += nt) lat[(size_t)m * W + i] = rounded[i];
-    if (kv.pages) store_row_to_pages<T>(kv, seq_slot[tok_seq[m]], tok_pos[m], W, rounded, t, nt);
+    if (kv.pages) store_row_to_pages<T>(kv, seq_slot[tok_seq[m]], tok_seq[m], tok_pos[m], W, rounded, t, nt);
     // the rotated part of every query head, in place
     if (q) {
         const int hd = plain + rot;
@@ -106,7 +110,7 @@ __global__ void latent_store_kernel(const T* __restrict__ lat, int W, const int*
     ti_pdl_sync();
     lat = ti_dependent(lat);
     const int m = blockIdx.x;
-    store_row_to_pages<T>(kv, seq_slot[tok_seq[m]], tok_pos[m], W, lat + (size_t)m * W, threadIdx.x, blockDim.x);
+    store_row_to_pages<T>(kv, seq_slot[tok_seq[m]], tok_seq[m], tok_pos[m], W, lat + (size_t)m * W, threadIdx.x, blockDim.x);
 }
 
 // ---------------------------------------------------------------------------
@@ -351,15 +355,15 @@ int launch_attn(const float* qa, const void* lat, float* ol, const int* cu_new, 
 // cos/sin: float32 [max_pos, rot / 2]; lat: [M, rank + rot] dense or null; pages null: no store.
 extern "C" int ti_latent_prep(const void* d, long long d_stride, void* q, long long q_stride, int n_heads, int plain,
                               int rank, int rot, const float* norm_w, float eps, const float* cos_t, const float* sin_t,
-                              int max_pos, const int* tok_pos, const int* tok_seq, const int* seq_slot, void* lat,
-                              void* pages, const int* page_table, int table_width, int page_size, int ring_rows, int n_pages,
+                              int max_pos, const int* tok_pos, const int* tok_seq, const int* seq_slot, const int* seq_len,
+                              void* lat, void* pages, const int* page_table, int table_width, int page_size, int ring_rows, int n_pages,
                               int M, int dtype, cudaStream_t stream) {
     if (M == 0) return 0;
     TI_REQUIRE(M > 0 && rank > 0 && rot >= 0 && rot % 2 == 0 && plain >= 0, "latent_prep: bad sizes");
     TI_REQUIRE(rot == 0 || (cos_t && sin_t && max_pos > 0), "latent_prep: a rotated part needs cos and sin tables");
-    TI_REQUIRE(!pages || (page_table && page_size > 0 && table_width > 0 && n_pages > 0 && ring_rows % page_size == 0),
+    TI_REQUIRE(!pages || (page_table && seq_len && page_size > 0 && table_width > 0 && n_pages > 0 && ring_rows % page_size == 0),
                "latent_prep: incomplete cache description");
-    LatentPages kv{pages, page_table, table_width, page_size, ring_rows, n_pages};
+    LatentPages kv{pages, page_table, table_width, page_size, ring_rows, n_pages, seq_len};
     const int W = rank + rot;
     return ti_dispatch_dtype(dtype, [&](auto t) -> int {
         using T = decltype(t);
@@ -374,12 +378,12 @@ extern "C" int ti_latent_prep(const void* d, long long d_stride, void* q, long l
 }
 
 extern "C" int ti_latent_store(const void* lat, int W, const int* tok_pos, const int* tok_seq, const int* seq_slot,
-                               void* pages, const int* page_table, int table_width, int page_size, int ring_rows, int n_pages,
+                               const int* seq_len, void* pages, const int* page_table, int table_width, int page_size, int ring_rows, int n_pages,
                                int M, int dtype, cudaStream_t stream) {
     if (M == 0) return 0;
-    TI_REQUIRE(pages && page_table && page_size > 0 && table_width > 0 && n_pages > 0 && ring_rows % page_size == 0,
+    TI_REQUIRE(pages && page_table && seq_len && page_size > 0 && table_width > 0 && n_pages > 0 && ring_rows % page_size == 0,
                "latent_store: incomplete cache description");
-    LatentPages kv{pages, page_table, table_width, page_size, ring_rows, n_pages};
+    LatentPages kv{pages, page_table, table_width, page_size, ring_rows, n_pages, seq_len};
     return ti_dispatch_dtype(dtype, [&](auto t) -> int {
         using T = decltype(t);
         TI_CUDA(ti_launch_class<2>(latent_store_kernel<T>, dim3(M), dim3(128), 0, stream, (const T*)lat, W, tok_pos, tok_seq,
@@ -434,7 +438,7 @@ extern "C" int ti_latent_attn(const float* qa, const void* lat, float* ol, const
     TI_REQUIRE(ring_rows == 0 || (window > 0 && ring_rows >= window),
                "latent_attention: a ring of %d rows needs a window of at most as many positions (got %d)", ring_rows, window);
     TI_REQUIRE(rank <= 1024, "latent_attention: a latent of %d elements is not supported (up to 1,024)", rank);
-    LatentPages kv{const_cast<void*>(pages), page_table, table_width, page_size, ring_rows, n_pages};
+    LatentPages kv{const_cast<void*>(pages), page_table, table_width, page_size, ring_rows, n_pages, nullptr};
     return ti_dispatch_dtype(dtype, [&](auto t) -> int {
         using T = decltype(t);
         if (rank <= 64)

@@ -53,9 +53,10 @@ def prep(d: torch.Tensor, q: Optional[torch.Tensor], rank: int, rot: int, norm_w
     if mem is not None:
         _check_mem(mem, W, d.dtype, "latent_prep")
     lat = torch.empty((M, W), dtype=d.dtype, device=d.device)
-    _call(_fn("ti_latent_prep", [P, L, P, L, I, I, I, I, P, F, P, P, I, P, P, P, P, P, P, I, I, I, I, I, I, P]),
+    _call(_fn("ti_latent_prep", [P, L, P, L, I, I, I, I, P, F, P, P, I, P, P, P, P, P, P, P, I, I, I, I, I, I, P]),
           _ptr(d), d.stride(0), _ptr(q), qs, nh, plain, rank, rot, _ptr(norm_w), float(eps), _ptr(cos), _ptr(sin), max_pos,
-          _ptr(batch.tok_pos), _ptr(batch.tok_seq), _ptr(batch.seq_slot), _ptr(lat), *_pages(mem), M, _code(d, "latent_prep"),
+          _ptr(batch.tok_pos), _ptr(batch.tok_seq), _ptr(batch.seq_slot), _ptr(batch.seq_len), _ptr(lat), *_pages(mem), M,
+          _code(d, "latent_prep"),
           _stream())
     return lat
 
@@ -64,8 +65,8 @@ def store(lat: torch.Tensor, batch, mem) -> None:
     """The step's rows to the cache."""
     M, W = lat.shape
     _check_mem(mem, W, lat.dtype, "latent_store")
-    _call(_fn("ti_latent_store", [P, I, P, P, P, P, P, I, I, I, I, I, I, P]), _ptr(lat), W, _ptr(batch.tok_pos),
-          _ptr(batch.tok_seq), _ptr(batch.seq_slot), *_pages(mem), M, _code(lat, "latent_store"), _stream())
+    _call(_fn("ti_latent_store", [P, I, P, P, P, P, P, P, I, I, I, I, I, I, P]), _ptr(lat), W, _ptr(batch.tok_pos),
+          _ptr(batch.tok_seq), _ptr(batch.seq_slot), _ptr(batch.seq_len), *_pages(mem), M, _code(lat, "latent_store"), _stream())
 
 
 def heads_per_block(n_heads: int, one_token_each: bool) -> int:
