@@ -78,13 +78,14 @@ def rotate(x: torch.Tensor, pos: int, freqs: Sequence[float], magnitude: float) 
 # ---------------------------------------------------------------------------
 # mixers (n: [T, width], one sequence from position 0)
 # ---------------------------------------------------------------------------
-def latent_attention(n: torch.Tensor, w: Dict[str, torch.Tensor], p: str, m: dict, eps: float) -> torch.Tensor:
+def latent_attention(n: torch.Tensor, w: Dict[str, torch.Tensor], p: str, m: dict, eps: float, start: int = 0) -> torch.Tensor:
+    """n: the rows of one sequence whose first row stands at position ``start`` (nothing before it is seen)."""
     T = n.shape[0]
     H, dim, rd, vd, rank = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
     window = int(m["mask"]["size"]) if m.get("mask") else 0
-    rot = m["rot"]
-    freqs, mag = scaled_frequencies(int(rot["dims"]), float(rot["base"]), rot.get("scaling"))
-    assert int(rot["dims"]) == rd
+    rot = m.get("rot")
+    freqs, mag = scaled_frequencies(int(rot["dims"]), float(rot["base"]), rot.get("scaling")) if rd else ([], 1.0)
+    assert not rd or int(rot["dims"]) == rd
     n = n.to(F64)
     q = (n @ w[p + "q"].to(F64).T).view(T, H, dim + rd)
     d = n @ w[p + "dkv"].to(F64).T
@@ -92,24 +93,20 @@ def latent_attention(n: torch.Tensor, w: Dict[str, torch.Tensor], p: str, m: dic
     r = d[:, rank:]
     uk = w[p + "uk"].to(F64).view(H, dim, rank)
     uv = w[p + "uv"].to(F64).view(H, vd, rank)
-    sink = w[p + "sink"].to(F64)
-    r_rot = torch.stack([rotate(r[t], t, freqs, mag) for t in range(T)])
+    sink = w[p + "sink"].to(F64) if (p + "sink") in w else None
+    r_rot = torch.stack([rotate(r[t], start + t, freqs, mag) for t in range(T)])
+    k_plain = torch.einsum("hdr,tr->thd", uk, c)          # every head's unrotated key part, per token
+    val = torch.einsum("hvr,tr->thv", uv, c)
     out = torch.zeros(T, H, vd, dtype=F64)
     for t in range(T):
         first = 0 if window <= 0 else max(0, t - window + 1)
         for h in range(H):
-            q_plain = q[t, h, :dim]
-            q_rot = rotate(q[t, h, dim:], t, freqs, mag)
-            s = []
-            for j in range(first, t + 1):
-                k_plain = uk[h] @ c[j]
-                s.append((q_plain @ k_plain + q_rot @ r_rot[j]) * m["scale"])
-            s = torch.stack(s)
-            top = torch.maximum(s.max(), sink[h])
+            q_rot = rotate(q[t, h, dim:], start + t, freqs, mag)
+            s = (k_plain[first:t + 1, h] @ q[t, h, :dim] + r_rot[first:t + 1] @ q_rot) * m["scale"]
+            top = s.max() if sink is None else torch.maximum(s.max(), sink[h])
             e = torch.exp(s - top)
-            denom = e.sum() + torch.exp(sink[h] - top)
-            for j in range(first, t + 1):
-                out[t, h] += e[j - first] / denom * (uv[h] @ c[j])
+            denom = e.sum() + (0.0 if sink is None else torch.exp(sink[h] - top))
+            out[t, h] = (e / denom) @ val[first:t + 1, h]
     return out.reshape(T, H * vd) @ w[p + "o"].to(F64).T
 
 

@@ -1,0 +1,153 @@
+"""Whole Kadodra models of several shapes through the engine against the plain implementation: whole prompts,
+token-by-token decoding, prompts in pieces and unequal batches under a random schedule with slots handed back and
+reused, greedy generation through the public entry point, and the trace runner."""
+from __future__ import annotations
+
+import json
+import os
+import random
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import ROOT
+from helpers import run_random_schedule
+from kadodra_cases import CASES, assert_close_logits, prompts, read_folder, write_folder
+from plain import kadodra_plain as plain
+
+pytestmark = pytest.mark.gpu
+DTYPES = ["float32", "bfloat16"]
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    return {name: write_folder(name, str(tmp_path_factory.mktemp(f"kadodra_{name}"))) for name in CASES}
+
+
+_plain = {}
+
+
+def plain_logits(folder, ids):
+    key = (folder, tuple(ids))
+    if key not in _plain:
+        if folder not in _plain:
+            _plain[folder] = read_folder(folder)
+        w, cfg = _plain[folder]
+        _plain[key] = plain.forward(w, cfg, ids)
+    return _plain[key]
+
+
+def engine(folder, dtype, **kw):
+    from toyinfer_b200.engine import Engine
+    kw.setdefault("max_tokens", 4096)
+    kw.setdefault("max_batch", 8)
+    kw.setdefault("max_seq_len", 512)
+    return Engine.from_folder(folder, dtype=dtype, **kw)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", list(CASES))
+def test_whole_prompts_of_unequal_lengths_in_one_step(folders, name, dtype):
+    eng = engine(folders[name], dtype)
+    ids = prompts(name, [1, 2, 65, 140, 7], seed=1)
+    slots = [eng.new_sequence() for _ in ids]
+    got = eng.step(list(zip(slots, ids)), [list(range(len(x))) for x in ids]).clone()
+    o = 0
+    for x in ids:
+        assert_close_logits(got[o:o + len(x)], plain_logits(folders[name], x), dtype, f"{name} prompt of {len(x)}")
+        o += len(x)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", list(CASES))
+def test_prompt_then_token_by_token(folders, name, dtype):
+    """Three sequences decode together after prompts of unequal lengths; the shortest ends early and its slot goes to a
+    new request that starts while the others go on... in a step of its own kind (starts do not mix with single tokens
+    here; the random schedule below mixes them)."""
+    eng = engine(folders[name], dtype)
+    ids = prompts(name, [150, 71, 9], seed=2)
+    heads = [70, 40, 3]
+    want = [plain_logits(folders[name], x) for x in ids]
+    slots = [eng.new_sequence() for _ in ids]
+    got = eng.step([(s, x[:h]) for s, x, h in zip(slots, ids, heads)], [[h - 1] for h in heads]).clone()
+    for i in range(3):
+        assert_close_logits(got[i:i + 1], want[i][heads[i] - 1:heads[i]], dtype, f"{name} prompt {i}")
+    fed = list(heads)
+    live = [0, 1, 2]
+    while live:
+        got = eng.step([(slots[i], [ids[i][fed[i]]]) for i in live]).clone()
+        for r, i in enumerate(live):
+            assert_close_logits(got[r:r + 1], want[i][fed[i]:fed[i] + 1], dtype, f"{name} seq {i} token {fed[i]}")
+            fed[i] += 1
+        for i in list(live):
+            if fed[i] == len(ids[i]):
+                eng.end_sequence(slots[i])
+                live.remove(i)
+    # the slots and pages come back: another request runs in them as if alone
+    again = prompts(name, [90], seed=3)[0]
+    s = eng.new_sequence()
+    assert s in slots
+    got = eng.step([(s, again)], [list(range(90))])
+    assert_close_logits(got, plain_logits(folders[name], again), dtype, f"{name} in a reused slot")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", list(CASES))
+def test_random_schedule_of_pieces_and_batches(folders, name, dtype):
+    eng = engine(folders[name], dtype, n_slots=4)
+    ids = prompts(name, [130, 67, 1, 5, 100, 64, 33], seed=4)
+    got = run_random_schedule(eng, ids, random.Random(11), max_live=4)
+    for x, g in zip(ids, got):
+        assert_close_logits(g, plain_logits(folders[name], x), dtype, f"{name} request of {len(x)}")
+    assert eng.cache.slots.n_free == 4
+
+
+@pytest.mark.parametrize("name", ["P", "Q"])
+def test_greedy_generation_through_the_public_entry(folders, name):
+    from toyinfer_b200 import LLM, SamplingParams
+    llm = LLM(folders[name], dtype="float32", max_seq_len=256, max_batch=4)
+    ids = prompts(name, [12, 40, 3], seed=5)
+    out = llm.generate(ids, SamplingParams(temperature=0.0), max_new_tokens=24)
+    w, cfg = read_folder(folders[name])
+    for x, r in zip(ids, out):
+        toks = list(r.tokens)
+        assert len(toks) == 24
+        seq = list(x)
+        for t in toks:
+            logits = plain.forward(w, cfg, seq)[-1]
+            top2 = torch.topk(logits, 2).values
+            if float(top2[0] - top2[1]) > 1e-3:         # a near tie may fall either way
+                assert int(torch.argmax(logits)) == t, (name, len(seq))
+            seq.append(t)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_trace_runner_on_a_folder(folders, tmp_path, dtype):
+    name = "Q"
+    V = CASES[name]["vocab"]
+    a, b = prompts(name, [100, 37], seed=6)
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": a[:90], "want": [0, 89]}, {"id": "b", "tokens": b[:30], "want": [29]}], "end": []}]
+    for k in range(10):
+        e = [{"id": "a", "tokens": [a[90 + k]], "want": [0]}]
+        if k < 7:
+            e.append({"id": "b", "tokens": [b[30 + k]], "want": [0] if k % 2 else []})
+        steps.append({"step": k + 1, "entries": e, "end": (["b"] if k == 6 else []) + (["a"] if k == 9 else [])})
+    out = str(tmp_path)
+    cmd = [sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", folders[name], "--dtype", dtype, "--out", out,
+           "--max-tokens", "256"]
+    p = subprocess.Popen(cmd, stdin=subprocess.PIPE, stdout=subprocess.PIPE, text=True)
+    for s in steps:
+        p.stdin.write(json.dumps(s) + "\n")
+        p.stdin.flush()
+        assert p.stdout.readline().strip() == f"done {s['step']}"
+    p.stdin.close()
+    assert p.wait(timeout=120) == 0
+    wa, wb = plain_logits(folders[name], a), plain_logits(folders[name], b)
+    read = lambda n: torch.from_numpy(np.fromfile(os.path.join(out, f"{n}.f32"), dtype="<f4").reshape(-1, V))
+    assert_close_logits(read(0), torch.stack([wa[0], wa[89], wb[29]]), dtype, "first step")
+    for k in range(10):
+        rows = [wa[90 + k]] + ([wb[30 + k]] if (k < 7 and k % 2) else [])
+        assert_close_logits(read(k + 1), torch.stack(rows), dtype, f"step {k + 1}")
