@@ -90,6 +90,10 @@ LATENT = [
     dict(heads=5, dim=16, rot=8, vdim=8, rank=24, window=37, scaling={"factor": 3.0, "original": 50, "fast": 6.0, "slow": 1.5}),
     dict(heads=2, dim=4, rot=16, vdim=24, rank=70, window=64, scaling=None),
     dict(heads=34, dim=6, rot=2, vdim=5, rank=10, window=5, scaling=None),
+    # heads that fill the tensor-core prompt kernel's 128 and 64 elements exactly, and ones that leave room
+    dict(heads=2, dim=64, rot=64, vdim=128, rank=64, window=100, scaling=None),
+    dict(heads=3, dim=32, rot=32, vdim=64, rank=32, window=0, scaling=None),
+    dict(heads=2, dim=40, rot=32, vdim=72, rank=16, window=65, scaling={"factor": 2.0, "original": 40, "fast": 4.0, "slow": 1.0}),
 ]
 
 
@@ -256,17 +260,19 @@ def test_squared_relu_feed_forward(dtype):
 
 @pytest.mark.parametrize("dtype", DT)
 @pytest.mark.parametrize("experts,top,M", [(5, 2, 70), (3, 1, 1), (4, 4, 9), (40, 3, 200)])
-def test_table_routed_experts(dtype, experts, top, M):
+@pytest.mark.parametrize("hidden,ff", [(40, 36), (136, 200)])
+def test_table_routed_experts(dtype, experts, top, M, hidden, ff):
+    """(Rows of 40 and 36 elements run on the CUDA cores in both types; 136 and 200 on the tensor cores in bfloat16.)"""
     from toyinfer_b200.parts import PartSpec, build_part
     vocab, limit = 23, 0.7
-    f = build_part("feed_forward", PartSpec("table_moe", {"n_experts": experts, "top": top, "intermediate_size": 36, "limit": limit,
-                                                          "vocab_size": vocab}), ctx_for(dtype, 40), "m.")
+    f = build_part("feed_forward", PartSpec("table_moe", {"n_experts": experts, "top": top, "intermediate_size": ff, "limit": limit,
+                                                          "vocab_size": vocab}), ctx_for(dtype, hidden), "m.")
     w = bind_random(f, 5, dtype)
     g = torch.Generator().manual_seed(6)
-    x = (4 * torch.randn(M, 40, generator=g)).to(dtype)          # large enough for both clamps to act
+    x = (4 * torch.randn(M, hidden, generator=g)).to(dtype)          # large enough for both clamps to act
     ids = torch.randint(0, vocab, (M,), generator=g).tolist()
     got = f.forward(x.to(DEV), batch_for("start", [0], [0], [M], 1, ids=[ids])).cpu().double()
-    cfg = {"router": {"experts": experts, "top": top}, "expert": {"ff": 36, "limit": limit}}
+    cfg = {"router": {"experts": experts, "top": top}, "expert": {"ff": ff, "limit": limit}}
     want = plain.table_moe(x.double(), ids, w, "m.", cfg)
     gate = x.double() @ w["m.e0.gate"].double().T
     assert (gate > limit).any() and (gate < -limit).any()

@@ -27,6 +27,7 @@
 //                  step buffer), any mix of starts and counts in one launch.
 //   latent_expand  o[m, h] = Wuv_h ol[m, h].
 #include "common.cuh"
+#include "attn_decode.cuh"
 
 namespace {
 
@@ -208,6 +209,34 @@ latent_expand_kernel(const float* __restrict__ ol, const T* __restrict__ uv, T* 
 }
 
 // ---------------------------------------------------------------------------
+// Keys and values per head after all, for steps of whole prompts on the tensor cores: from the up-projection's output
+// ku[m] = [Wuk c | Wuv c] (heads * plain, then heads * vdim) and the step's rows, the padded heads
+//     Q[m, h] = [q plain | q rotated | 0],  K[m, h] = [Wuk_h c | r | 0],  V[m, h] = [Wuv_h c | 0]      (D elements each)
+// that a plain multi-head attention kernel takes.  One block per token.
+template <typename T>
+__global__ void latent_pack_kernel(const T* __restrict__ q, long long q_stride, const T* __restrict__ ku, const T* __restrict__ lat,
+                                   T* __restrict__ Qp, T* __restrict__ Kp, T* __restrict__ Vp, int n_heads, int plain, int rot,
+                                   int vdim, int rank, int D) {
+    ti_pdl_trigger();
+    ti_pdl_sync();
+    q = ti_dependent(q); ku = ti_dependent(ku); lat = ti_dependent(lat);
+    const size_t m = blockIdx.x;
+    const int hd = plain + rot, W = rank + rot;
+    const T* qrow = q + m * q_stride;
+    const T* krow = ku + m * ((size_t)n_heads * (plain + vdim));
+    const T* vrow = krow + (size_t)n_heads * plain;
+    const T* rrow = lat + m * W + rank;
+    const T zero = from_f32<T>(0.f);
+    for (int idx = threadIdx.x; idx < n_heads * D; idx += blockDim.x) {
+        const int h = idx / D, e = idx - h * D;
+        const size_t o = (m * n_heads + h) * D + e;
+        Qp[o] = e < hd ? qrow[(size_t)h * hd + e] : zero;
+        Kp[o] = e < plain ? krow[(size_t)h * plain + e] : e < hd ? rrow[e - plain] : zero;
+        Vp[o] = e < vdim ? vrow[(size_t)h * vdim + e] : zero;
+    }
+}
+
+// ---------------------------------------------------------------------------
 // The attention.  A block works on 32 rows = QB consecutive queries of a sequence times HB heads
 // (HB * QB == 32) against key tiles of 32 positions; thread t works on row t / 4, its 4 threads split
 // a tile's keys (scores) and the latent's elements (output) between them.
@@ -218,7 +247,7 @@ __global__ void __launch_bounds__(LTHREADS)
 latent_attn_kernel(const float* __restrict__ qa, const T* __restrict__ lat, float* __restrict__ ol,
                    const int* __restrict__ cu_new, const int* __restrict__ seq_start, const int* __restrict__ seq_slot,
                    int n_heads, int hb, int rank, int rot, float scale, int window, const float* __restrict__ sink,
-                   LatentPages kv) {
+                   LatentPages kv, int n_splits, float* __restrict__ part_o, float* __restrict__ part_ml) {
     ti_pdl_trigger();
     extern __shared__ float sm[];
     ti_pdl_sync();
@@ -228,7 +257,10 @@ latent_attn_kernel(const float* __restrict__ qa, const T* __restrict__ lat, floa
     float* Ks = Qs + LQ * ld;             // [LK][ld]
     float* Ps = Ks + LK * ld;             // [LQ][LK + 1]
     const int qb = LQ / hb;
-    const int b = blockIdx.z, h0 = blockIdx.y * hb, q0 = blockIdx.x * qb;
+    // with n_splits > 1 the key tiles of a block's queries are shared out over n_splits blocks, which leave their
+    // unnormalised sums, maxima and denominators for the merging kernel
+    const int split = blockIdx.x % n_splits;
+    const int b = blockIdx.z, h0 = blockIdx.y * hb, q0 = (blockIdx.x / n_splits) * qb;
     const int tok0 = cu_new[b];
     const int n = cu_new[b + 1] - tok0;
     if (q0 >= n) return;
@@ -248,26 +280,29 @@ latent_attn_kernel(const float* __restrict__ qa, const T* __restrict__ lat, floa
     for (int c = 0; c < MAXC; c++) acc[c] = 0.f;
     // the sink stands in the denominator from the start: running maximum sink_h, running sum 1
     float m_run = -INFINITY, l_run = 0.f;
-    if (sink && row_ok) { m_run = sink[my_h]; l_run = 1.f; }
+    if (sink && row_ok && split == 0) { m_run = sink[my_h]; l_run = 1.f; }
     const int nc = (rank + 3) >> 2;      // elements of the latent per thread (c4 + 4 c)
     const int last_q = start + min(q0 + qb, n) - 1;
     const int lo = window > 0 ? max(0, start + q0 - window + 1) : 0;
-    for (int k0 = (lo / LK) * LK; k0 <= last_q; k0 += LK) {
+    const int kt_first = lo / LK, kt_last = last_q / LK;
+    const int per = (kt_last - kt_first + n_splits) / n_splits;
+    const int kt_a = kt_first + split * per, kt_b = min(kt_last, kt_a + per - 1);
+    for (int kt = kt_a; kt <= kt_b; kt++) {
+        const int k0 = kt * LK;
         __syncthreads();
-        for (int idx = t; idx < LK * W; idx += LTHREADS) {
-            const int rr = idx / W, e = idx - rr * W;
+        // a warp fetches whole rows: where a row lives is worked out once, then the lanes run along it
+        for (int rr = t >> 5; rr < LK; rr += LTHREADS / 32) {
             const int p = k0 + rr;
-            float x = 0.f;
+            const T* src = nullptr;
             if (p >= start) {
-                if (p < end) x = to_f32(lat[(size_t)(tok0 + p - start) * W + e]);
+                if (p < end) src = lat + (size_t)(tok0 + p - start) * W;
             } else if (p >= lo) {
                 const int row = kv.ring_rows > 0 ? p % kv.ring_rows : p;
                 const int pidx = row / kv.page_size;
                 const int page = pidx < kv.table_width ? kv.page_table[(size_t)slot * kv.table_width + pidx] : -1;
-                if (page >= 0 && page < kv.n_pages)
-                    x = to_f32(((const T*)kv.pages)[((size_t)page * kv.page_size + row % kv.page_size) * W + e]);
+                if (page >= 0 && page < kv.n_pages) src = (const T*)kv.pages + ((size_t)page * kv.page_size + row % kv.page_size) * W;
             }
-            Ks[rr * ld + e] = x;
+            for (int e = t & 31; e < W; e += 32) Ks[rr * ld + e] = src ? to_f32(src[e]) : 0.f;
         }
         __syncthreads();
         float s[8];
@@ -320,7 +355,13 @@ latent_attn_kernel(const float* __restrict__ qa, const T* __restrict__ lat, floa
                 if (c < nc) acc[c] = fmaf(p, vrow[4 * c], acc[c]);      // (an element past the rank is the rotated part: never stored)
         }
     }
-    if (row_ok) {
+    if (row_ok && n_splits > 1) {
+        const size_t at = ((size_t)(tok0 + my_q) * n_heads + my_h) * n_splits + split;
+        if (c4 == 0) { part_ml[at * 2] = m_run; part_ml[at * 2 + 1] = l_run; }
+#pragma unroll
+        for (int c = 0; c < MAXC; c++)
+            if (c < nc && c4 + 4 * c < rank) part_o[at * rank + c4 + 4 * c] = acc[c];
+    } else if (row_ok) {
         const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
         float* orow = ol + ((size_t)(tok0 + my_q) * n_heads + my_h) * rank;
 #pragma unroll
@@ -332,7 +373,7 @@ latent_attn_kernel(const float* __restrict__ qa, const T* __restrict__ lat, floa
 template <typename T, int MAXC>
 int launch_attn(const float* qa, const void* lat, float* ol, const int* cu_new, const int* seq_start, const int* seq_slot,
                 int n_seq, int max_new, int n_heads, int hb, int rank, int rot, float scale, int window, const float* sink,
-                const LatentPages& kv, cudaStream_t stream) {
+                const LatentPages& kv, int n_splits, float* part_o, float* part_ml, int n_tok, cudaStream_t stream) {
     const int W = rank + rot;
     const size_t smem = ((size_t)(LQ + LK) * (W + 1) + (size_t)LQ * (LK + 1)) * sizeof(float);
     TI_REQUIRE(smem <= 227 * 1024, "latent_attention: rows of %d elements need %zu bytes of shared memory", W, smem);
@@ -342,10 +383,17 @@ int launch_attn(const float* qa, const void* lat, float* ol, const int* cu_new, 
         configured = smem;
     }
     const int qb = LQ / hb;
-    dim3 grid((max_new + qb - 1) / qb, (n_heads + hb - 1) / hb, n_seq);
+    dim3 grid(((max_new + qb - 1) / qb) * n_splits, (n_heads + hb - 1) / hb, n_seq);
     TI_CUDA(ti_launch(latent_attn_kernel<T, MAXC>, grid, dim3(LTHREADS), smem, stream, qa, (const T*)lat, ol, cu_new, seq_start,
-                      seq_slot, n_heads, hb, rank, rot, scale, window, sink, kv));
+                      seq_slot, n_heads, hb, rank, rot, scale, window, sink, kv, n_splits, part_o, part_ml));
     TI_CHECK_LAUNCH("latent_attention");
+    if (n_splits > 1) {
+        // the splits' sums meet: one block per (token, head), the latent's elements over its threads
+        int threads = ((rank + 3) / 4 + 31) / 32 * 32;
+        TI_CUDA(ti_launch_class<4>(tiattn::attn_decode_combine_kernel<float>, dim3(n_tok, n_heads), dim3(threads), 0, stream,
+                                   (const float*)part_o, (const float*)part_ml, ol, (long long)n_heads * rank, n_heads, rank, n_splits));
+        TI_CHECK_LAUNCH("latent_attention_combine");
+    }
     return 0;
 }
 
@@ -393,6 +441,20 @@ extern "C" int ti_latent_store(const void* lat, int W, const int* tok_pos, const
     });
 }
 
+extern "C" int ti_latent_pack(const void* q, long long q_stride, const void* ku, const void* lat, void* Qp, void* Kp, void* Vp,
+                              int M, int n_heads, int plain, int rot, int vdim, int rank, int D, int dtype, cudaStream_t stream) {
+    if (M == 0) return 0;
+    TI_REQUIRE(M > 0 && n_heads > 0 && plain >= 0 && rot >= 0 && vdim > 0 && rank > 0 && D >= plain + rot && D >= vdim,
+               "latent_pack: heads of %d + %d and %d elements do not fit %d", plain, rot, vdim, D);
+    return ti_dispatch_dtype(dtype, [&](auto t) -> int {
+        using T = decltype(t);
+        TI_CUDA(ti_launch_class<2>(latent_pack_kernel<T>, dim3(M), dim3(256), 0, stream, (const T*)q, q_stride, (const T*)ku,
+                                   (const T*)lat, (T*)Qp, (T*)Kp, (T*)Vp, n_heads, plain, rot, vdim, rank, D));
+        TI_CHECK_LAUNCH("latent_pack");
+        return 0;
+    });
+}
+
 extern "C" int ti_latent_absorb(const void* q, long long q_stride, const void* uk, float* qa, int M, int n_heads, int plain,
                                 int rank, int rot, int dtype, cudaStream_t stream) {
     if (M == 0) return 0;
@@ -428,7 +490,8 @@ extern "C" int ti_latent_expand(const float* ol, const void* uv, void* o, long l
 extern "C" int ti_latent_attn(const float* qa, const void* lat, float* ol, const int* cu_new, const int* seq_start,
                               const int* seq_slot, int n_seq, int max_new, int n_heads, int hb, int rank, int rot, float scale,
                               int window, const float* sink, const void* pages, const int* page_table, int table_width,
-                              int page_size, int ring_rows, int n_pages, int dtype, cudaStream_t stream) {
+                              int page_size, int ring_rows, int n_pages, int n_splits, float* part_o, float* part_ml, int n_tok,
+                              int dtype, cudaStream_t stream) {
     if (n_seq == 0 || max_new == 0) return 0;
     TI_REQUIRE(n_seq > 0 && max_new > 0 && n_heads > 0 && rank > 0 && rot >= 0, "latent_attention: bad sizes");
     TI_REQUIRE(hb >= 1 && hb <= LQ && (hb & (hb - 1)) == 0, "latent_attention: %d heads per block (a power of two up to %d)", hb, LQ);
@@ -438,17 +501,19 @@ extern "C" int ti_latent_attn(const float* qa, const void* lat, float* ol, const
     TI_REQUIRE(ring_rows == 0 || (window > 0 && ring_rows >= window),
                "latent_attention: a ring of %d rows needs a window of at most as many positions (got %d)", ring_rows, window);
     TI_REQUIRE(rank <= 1024, "latent_attention: a latent of %d elements is not supported (up to 1,024)", rank);
+    TI_REQUIRE(n_splits >= 1 && (n_splits == 1 || (part_o && part_ml && n_tok > 0 && n_tok <= 65535 * 32768)),
+               "latent_attention: %d splits need room for their partial results", n_splits);
     LatentPages kv{const_cast<void*>(pages), page_table, table_width, page_size, ring_rows, n_pages, nullptr};
     return ti_dispatch_dtype(dtype, [&](auto t) -> int {
         using T = decltype(t);
         if (rank <= 64)
-            return launch_attn<T, 16>(qa, lat, ol, cu_new, seq_start, seq_slot, n_seq, max_new, n_heads, hb, rank, rot, scale, window, sink, kv, stream);
+            return launch_attn<T, 16>(qa, lat, ol, cu_new, seq_start, seq_slot, n_seq, max_new, n_heads, hb, rank, rot, scale, window, sink, kv, n_splits, part_o, part_ml, n_tok, stream);
         if (rank <= 128)
-            return launch_attn<T, 32>(qa, lat, ol, cu_new, seq_start, seq_slot, n_seq, max_new, n_heads, hb, rank, rot, scale, window, sink, kv, stream);
+            return launch_attn<T, 32>(qa, lat, ol, cu_new, seq_start, seq_slot, n_seq, max_new, n_heads, hb, rank, rot, scale, window, sink, kv, n_splits, part_o, part_ml, n_tok, stream);
         if (rank <= 256)
-            return launch_attn<T, 64>(qa, lat, ol, cu_new, seq_start, seq_slot, n_seq, max_new, n_heads, hb, rank, rot, scale, window, sink, kv, stream);
+            return launch_attn<T, 64>(qa, lat, ol, cu_new, seq_start, seq_slot, n_seq, max_new, n_heads, hb, rank, rot, scale, window, sink, kv, n_splits, part_o, part_ml, n_tok, stream);
         if (rank <= 512)
-            return launch_attn<T, 128>(qa, lat, ol, cu_new, seq_start, seq_slot, n_seq, max_new, n_heads, hb, rank, rot, scale, window, sink, kv, stream);
-        return launch_attn<T, 256>(qa, lat, ol, cu_new, seq_start, seq_slot, n_seq, max_new, n_heads, hb, rank, rot, scale, window, sink, kv, stream);
+            return launch_attn<T, 128>(qa, lat, ol, cu_new, seq_start, seq_slot, n_seq, max_new, n_heads, hb, rank, rot, scale, window, sink, kv, n_splits, part_o, part_ml, n_tok, stream);
+        return launch_attn<T, 256>(qa, lat, ol, cu_new, seq_start, seq_slot, n_seq, max_new, n_heads, hb, rank, rot, scale, window, sink, kv, n_splits, part_o, part_ml, n_tok, stream);
     });
 }

@@ -49,6 +49,7 @@ struct Args {
     void* out; long long o_stride;
     // PAGED form: where the positions before the step's tokens are kept
     const int* seq_start; const int* seq_slot; const int* page_table; int table_width, ring_rows, n_pages;
+    const float* sink;      // per head a logit that stands in the softmax's denominator without key or value (not scaled); or null
 };
 
 __device__ __forceinline__ float ex2(float x) {
@@ -418,6 +419,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
         l_s[half * BQ + r] = l_run;
         asm volatile("bar.sync %0, 64;" ::"r"(1 + qd) : "memory");      // the two warps that share these rows
         l_run += l_s[(half ^ 1) * BQ + r];
+        // the sink joins the denominator in the units of the sums: 2^(sink * log2(e) - m)
+        if (a.sink != nullptr && m_used > -INFINITY) l_run += ex2(fminf(a.sink[h] * 1.4426950408889634f - m_used, 126.f));
         if (ok) {
             tc_fence_after();
             const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
@@ -521,6 +524,22 @@ extern "C" int ti_attn_prefill_tc(const void* q, const void* k, const void* v, v
     Args a = {};
     a.cu_new = cu_new; a.n_heads = n_heads; a.n_kv_heads = n_kv_heads; a.scale = scale; a.window = window;
     a.out = out; a.o_stride = o_stride;
+    return head_dim == 64 ? launch<64, false>(qm, km, vm, km, vm, a, n_seq, max_new, stream)
+                          : launch<128, false>(qm, km, vm, km, vm, a, n_seq, max_new, stream);
+}
+
+// The same with sinks: float32 sink[n_heads], exp(sink_h) is added to head h's softmax denominator.
+extern "C" int ti_attn_prefill_tc_sink(const void* q, const void* k, const void* v, void* out,
+                                       long long q_stride, long long k_stride, long long v_stride, long long o_stride,
+                                       const int* cu_new, int n_seq, int max_new, int n_tokens, int n_heads, int n_kv_heads,
+                                       int head_dim, float scale, int window, const float* sink, cudaStream_t stream) {
+    if (n_seq == 0 || max_new == 0) return 0;
+    CUtensorMap qm, km, vm;
+    if (int rc = check_common("attention_prefill", q, k, v, out, q_stride, k_stride, v_stride, o_stride, n_seq, n_tokens,
+                              n_heads, n_kv_heads, head_dim, &qm, &km, &vm)) return rc;
+    Args a = {};
+    a.cu_new = cu_new; a.n_heads = n_heads; a.n_kv_heads = n_kv_heads; a.scale = scale; a.window = window;
+    a.out = out; a.o_stride = o_stride; a.sink = sink;
     return head_dim == 64 ? launch<64, false>(qm, km, vm, km, vm, a, n_seq, max_new, stream)
                           : launch<128, false>(qm, km, vm, km, vm, a, n_seq, max_new, stream);
 }

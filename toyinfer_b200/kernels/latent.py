@@ -79,6 +79,58 @@ def heads_per_block(n_heads: int, one_token_each: bool) -> int:
     return hb
 
 
+def decode_splits(n_seq: int, n_heads: int, hb: int, span: int, sms: int) -> int:
+    """Blocks that share a sequence's keys when every sequence brings one query: about two blocks per SM in all, a tile
+    of 32 keys each at least, 64 at most."""
+    tiles = span // 32 + 2
+    groups = (n_heads + hb - 1) // hb
+    return max(1, min((2 * sms) // max(1, n_seq * groups), tiles, 64))
+
+
+def plan(n_seq: int, n_heads: int, window: int, plan_len: int, device) -> int:
+    """The splits of a step of single tokens planned for ``plan_len`` positions (what of its launches depends on the length)."""
+    from .gemm import sm_count
+    span = plan_len if window <= 0 else min(plan_len, window)
+    return decode_splits(n_seq, n_heads, heads_per_block(n_heads, True), span, sm_count(device))
+
+
+def prompt_heads(plain: int, rot: int, vdim: int) -> int:
+    """The head size (64 or 128) at which a step of whole prompts runs as plain multi-head attention on the tensor cores,
+    or 0 when the heads do not fit."""
+    need = max(plain + rot, vdim)
+    return 64 if need <= 64 else 128 if need <= 128 else 0
+
+
+def attention_prompt(q: torch.Tensor, lat: torch.Tensor, w_ukv: torch.Tensor, vdim: int, rank: int, rot: int, scale: float,
+                     window: int, sink: Optional[torch.Tensor], batch, D: int) -> torch.Tensor:
+    """Every sequence starts at position 0, bfloat16: keys and values per head are formed from the step's rows by one product
+    with w_ukv = [Wuk; Wuv], packed beside the queries into heads of D elements, and a multi-head attention over the step's own
+    tokens runs on the tensor cores.  Returns [M, heads * D]: head h's value in its first ``vdim`` elements, zeros after."""
+    from . import linear
+    from .lib import library
+    M, nh, hd = q.shape
+    plain = hd - rot
+    ku = linear(lat[:, :rank], w_ukv)                    # [M, heads * plain + heads * vdim]
+    Qp = torch.empty((M, nh, D), dtype=q.dtype, device=q.device)
+    Kp, Vp, out = torch.empty_like(Qp), torch.empty_like(Qp), torch.empty_like(Qp)
+    _call(_fn("ti_latent_pack", [P, L, P, P, P, P, P, I, I, I, I, I, I, I, I, P]), _ptr(q), q.stride(0), _ptr(ku), _ptr(lat),
+          _ptr(Qp), _ptr(Kp), _ptr(Vp), M, nh, plain, rot, vdim, rank, D, _code(q, "latent_pack"), _stream())
+    _call(_fn("ti_attn_prefill_tc_sink", [P, P, P, P, L, L, L, L, P, I, I, I, I, I, I, F, I, P, P]),
+          _ptr(Qp), _ptr(Kp), _ptr(Vp), _ptr(out), nh * D, nh * D, nh * D, nh * D, _ptr(batch.cu_new), batch.n_seq, batch.max_new,
+          M, nh, nh, D, float(scale), int(window), _ptr(sink), _stream())
+    return out.view(M, nh * D)
+
+
+def prompt_eligible(q: torch.Tensor, lat: torch.Tensor, rank: int, rot: int, vdim: int, batch) -> int:
+    """The head size for attention_prompt, or 0: bfloat16, every sequence at its start, heads that fit, and rows the
+    tensor-core product takes (16-byte pieces)."""
+    if q.dtype != torch.bfloat16 or batch.mode != "start":
+        return 0
+    if rank % 8 or (rank + rot) % 8 or lat.data_ptr() % 16:
+        return 0
+    return prompt_heads(q.shape[2] - rot, rot, vdim)
+
+
 def attention(q: torch.Tensor, lat: torch.Tensor, uk: torch.Tensor, uv: torch.Tensor, vdim: int, rank: int, rot: int,
               scale: float, window: int, sink: Optional[torch.Tensor], batch, mem) -> torch.Tensor:
     """q[M, heads, plain + rot] (rotated part already rotated), the step's rows lat[M, rank + rot], uk[heads * plain, rank],
@@ -100,9 +152,16 @@ def attention(q: torch.Tensor, lat: torch.Tensor, uk: torch.Tensor, uv: torch.Te
           rank, rot, code, _stream())
     ol = torch.empty((M, nh, rank), dtype=torch.float32, device=q.device)
     hb = heads_per_block(nh, batch.mode == "extend")
-    _call(_fn("ti_latent_attn", [P, P, P, P, P, P, I, I, I, I, I, I, F, I, P, P, P, I, I, I, I, I, P]),
+    splits, part_o, part_ml = 1, None, None
+    if batch.mode == "extend":
+        splits = plan(batch.n_seq, nh, window, batch.plan_len, q.device)
+        if splits > 1:
+            part_o = torch.empty((M, nh, splits, rank), dtype=torch.float32, device=q.device)
+            part_ml = torch.empty((M, nh, splits, 2), dtype=torch.float32, device=q.device)
+    _call(_fn("ti_latent_attn", [P, P, P, P, P, P, I, I, I, I, I, I, F, I, P, P, P, I, I, I, I, I, P, P, I, I, P]),
           _ptr(qa), _ptr(lat), _ptr(ol), _ptr(batch.cu_new), _ptr(batch.seq_start), _ptr(batch.seq_slot), batch.n_seq,
-          batch.max_new, nh, hb, rank, rot, float(scale), int(window), _ptr(sink), *_pages(mem), code, _stream())
+          batch.max_new, nh, hb, rank, rot, float(scale), int(window), _ptr(sink), *_pages(mem), splits, _ptr(part_o),
+          _ptr(part_ml), M, code, _stream(), launches=2 if splits > 1 else 1)
     o = torch.empty((M, nh * vdim), dtype=q.dtype, device=q.device)
     _call(_fn("ti_latent_expand", [P, P, P, L, I, I, I, I, I, P]), _ptr(ol), _ptr(uv), _ptr(o), o.stride(0), M, nh, vdim, rank,
           code, _stream())

@@ -72,6 +72,18 @@ class LatentAttention(Mixer):
         self.w_uk = tensors.pop(self.names["uk"]).contiguous()
         self.w_uv = tensors.pop(self.names["uv"]).contiguous()
         self.w_o = tensors.pop(self.names["o"]).contiguous()
+        # for steps of whole prompts on the tensor cores: both up-projections as one matrix, and the output projection
+        # with columns of zeros where a head of D elements holds nothing
+        self.w_ukv = self.w_o_padded = None
+        D = KL.prompt_heads(self.dim, self.rot, self.vdim)
+        if self.w_o.dtype == torch.bfloat16 and D:
+            self.w_ukv = torch.cat([self.w_uk, self.w_uv], dim=0).contiguous()
+            if D == self.vdim:
+                self.w_o_padded = self.w_o
+            else:
+                wide = torch.zeros((self.hidden, self.n_heads, D), dtype=self.w_o.dtype, device=self.w_o.device)
+                wide[:, :, : self.vdim] = self.w_o.view(self.hidden, self.n_heads, self.vdim)
+                self.w_o_padded = wide.view(self.hidden, self.n_heads * D).contiguous()
         self.norm_w = tensors.pop(self.names["dkv_norm"]).to(torch.float32).contiguous()
         self.sink = tensors.pop(self.names["sink"]).to(torch.float32).contiguous() if self.sinks else None
 
@@ -86,7 +98,7 @@ class LatentAttention(Mixer):
         return KVRequest(1, self.rank + self.rot, self.window, values=False)
 
     def launch_plan(self, n_seq: int, plan_len: int, dtype, device, n_live=None):
-        return ("latent",)          # nothing of the launches looks at the planned length
+        return ("latent", KL.plan(n_seq, self.n_heads, self.window, plan_len, device))    # the split of a sequence's keys over blocks
 
     def forward(self, x, batch, mem, shared) -> torch.Tensor:
         if mem is None or not hasattr(mem, "k_pages"):
@@ -103,12 +115,17 @@ class LatentAttention(Mixer):
             store_first = not (batch.mode == "mixed" and mem.ring_rows > 0)
             tables = self.pos.rotary_tables() if self.pos is not None else None
             lat = KL.prep(d, q, self.rank, self.rot, self.norm_w, self.eps, tables, batch, mem if store_first else None)
-            a = KL.attention(q, lat, self.w_uk, self.w_uv, self.vdim, self.rank, self.rot, self.scale, self.window,
-                             self.sink, batch, mem)
+            D = KL.prompt_eligible(q, lat, self.rank, self.rot, self.vdim, batch) if self.w_ukv is not None else 0
+            if D:
+                a = KL.attention_prompt(q, lat, self.w_ukv, self.vdim, self.rank, self.rot, self.scale, self.window,
+                                        self.sink, batch, D)
+            else:
+                a = KL.attention(q, lat, self.w_uk, self.w_uv, self.vdim, self.rank, self.rot, self.scale, self.window,
+                                 self.sink, batch, mem)
             if not store_first:
                 KL.store(lat, batch, mem)
         with ranged(batch, "mixer.out"):
-            return K.linear(a, self.w_o)
+            return K.linear(a, self.w_o_padded if D else self.w_o)
 
 
 register_part("mixer", "latent_attention", LatentAttention)
