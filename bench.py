@@ -448,6 +448,82 @@ def run_prompt_steps(lengths, layers: int):
                           "captured": eng.graph_replays - replays == 5}), flush=True)
 
 
+# ---------------------------------------------------------------------------
+# another design beside the closest existing model at equal size
+# ---------------------------------------------------------------------------
+def _kadodra_config(width, heads, layers, kind, vocab=32000):
+    """``layers`` equal layers of one kind: "latent" (latent attention with a window, sinks and stretched rotation, beside a
+    squared-ReLU feed-forward) or "lightning" (linear attention with a decayed state, beside table-routed experts)."""
+    if kind == "latent":
+        layer = {"type": "latent_attention",
+                 "mixer": {"heads": heads, "dim": 64, "rot_dim": 64, "vdim": 128, "kv_rank": 512, "scale": 128 ** -0.5,
+                           "mask": {"size": width // 2},
+                           "rot": {"base": 1e6, "dims": 64, "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}},
+                 "mlp": {"kind": "dense", "ff": 4 * width}}
+    else:
+        layer = {"type": "lightning",
+                 "mixer": {"heads": heads, "dim": 128, "vdim": 128, "decay": [1.0 - 2.0 ** -(2 + 6 * h / heads) for h in range(heads)]},
+                 "mlp": {"kind": "moe", "expert": {"ff": width, "limit": 7.0}, "router": {"experts": 16, "top": 2}}}
+    return {"architecture": "Kadodra", "vocab": vocab, "width": width, "logit_scale": 1.0, "norm": {"eps": 1e-6},
+            "layers": [json.loads(json.dumps(layer)) for _ in range(layers)], "max_positions": 8192}
+
+
+def _qwen3_like(width, heads, layers, vocab=32000):
+    """The dense model of the same width, head count and layers; its three feed-forward matrices of 8/3 width hold what the
+    other design's two of 4 width (or its two active experts of three matrices each, 6 width... the nearest round size) hold."""
+    return {"architectures": ["Qwen3ForCausalLM"], "num_hidden_layers": layers, "hidden_size": width, "num_attention_heads": heads,
+            "num_key_value_heads": max(1, heads // 4), "head_dim": 128, "intermediate_size": width * 8 // 3 // 128 * 128,
+            "vocab_size": vocab, "rope_theta": 1e6, "rms_norm_eps": 1e-6, "max_position_embeddings": 8192, "tie_word_embeddings": True}
+
+
+def run_design(name: str, widths, layers: int, tokens: int, batch: int, context: int):
+    """Prompt and decode rates of another design at layer sizes of a real model (random weights, bfloat16) beside the dense
+    model at equal size, with the device time of every stage of a layer (plain launches, CUDA events).  One JSON line per
+    model: a prompt of ``tokens`` tokens (best of three), ``batch`` sequences decoding at ``context`` positions (replayed
+    graphs, mean of 32 steps), and per stage the mean milliseconds per layer in a prompt step and in a decode step."""
+    import torch
+    from toyinfer_b200.engine import Engine
+    from toyinfer_b200.tracing import Tracer
+    if name != "kadodra":
+        raise SystemExit(f"bench.py: unknown design {name!r} (kadodra)")
+    for width in widths:
+        heads = width // 128
+        models = [("kadodra latent+dense", _kadodra_config(width, heads, layers, "latent")),
+                  ("kadodra lightning+experts", _kadodra_config(width, heads, layers, "lightning")),
+                  ("qwen3 dense", _qwen3_like(width, heads, layers))]
+        for label, cfg in models:
+            kw = dict(seed=0, dtype="bfloat16", max_tokens=batch * (context + 64) + tokens + 64, max_batch=batch, max_seq_len=context + 64)
+            sampler = ClockSampler()
+            sampler.start()
+            eng = Engine.from_config(cfg, **kw)
+            prefill_ms = time_prefill(eng, tokens)
+            decode_ms, launches = time_decode(eng, batch, context, 32, 8)
+            clocks = sampler.stop()
+            del eng
+            torch.cuda.empty_cache()
+            # the stages, from plain launches with events around them
+            tr = Tracer(nvtx=False, timing=True)
+            eng = Engine.from_config(cfg, use_cuda_graph=False, tracer=tr, **kw)
+            time_prefill(eng, tokens, reps=1)
+            tr.reset()
+            time_prefill(eng, tokens, reps=2)
+            torch.cuda.synchronize()
+            n_layers = len(eng.model.schedule)
+            pre = {k: round(ms / max(c, 1), 4) for k, (c, ms) in tr.report().items()}
+            tr.reset()
+            time_decode(eng, batch, min(context, 512 + 16), 8, 8)
+            torch.cuda.synchronize()
+            dec = {k: round(ms / max(c, 1), 4) for k, (c, ms) in tr.report().items()}
+            weights = sum(math.prod(sp.shape) for sp in eng.model.param_specs().values())
+            del eng
+            torch.cuda.empty_cache()
+            print(json.dumps({"design": label, "width": width, "heads": heads, "layers": n_layers, "weights_m": round(weights / 1e6, 1),
+                              "prompt_tokens": tokens, "prompt_ms": round(prefill_ms, 3), "prompt_tokens_per_s": round(tokens / prefill_ms * 1e3, 1),
+                              "decode_batch": batch, "decode_context": context, "decode_ms_per_step": round(decode_ms, 4),
+                              "decode_tokens_per_s": round(batch / decode_ms * 1e3, 1), "decode_launches": launches,
+                              "stage_ms_prompt": pre, "stage_ms_decode_at_512": dec, "clocks": clocks}), flush=True)
+
+
 def run_mma_issue():
     """Cycles per tcgen05 MMA of 128 x N x 16 as one issuing thread per block sees them, with the thread
     chosen by ``lane == 0`` and by ``elect.sync`` in a warp-uniform branch, one and two blocks per SM
@@ -623,6 +699,10 @@ def main() -> int:
                     help="run one of the larger described workloads end to end instead (8B or 32B shape)")
     ap.add_argument("--prompt-steps", default="", help="time one prompt step of each of these lengths instead (comma-separated), "
                     "with --layers layers")
+    ap.add_argument("--design", default="", help="measure another design beside the dense model at equal size instead: kadodra "
+                    "(with --widths, --layers, --tokens, --batch, --context)")
+    ap.add_argument("--widths", default="2048,4096", help="with --design: model widths (heads of 128)")
+    ap.add_argument("--tokens", type=int, default=PREFILL_TOKENS, help="with --design: the prompt's tokens")
     ap.add_argument("--reps", type=int, default=20)
     ap.add_argument("--eager", action="store_true", help="with --kernel: plain launches instead of a graph replay")
     args = ap.parse_args()
@@ -644,6 +724,10 @@ def main() -> int:
         return 0
     if args.workload:
         print(json.dumps(run_workload(args.workload)))
+        return 0
+    if args.design:
+        run_design(args.design, [int(v) for v in args.widths.split(",")], args.layers if args.layers != FULL_LAYERS else 4,
+                   args.tokens, args.batch, args.context if args.context != CONTEXT else 2048)
         return 0
     if args.prompt_steps:
         run_prompt_steps([int(v) for v in args.prompt_steps.split(",")], args.layers)

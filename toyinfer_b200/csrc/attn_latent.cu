@@ -117,7 +117,7 @@ __global__ void latent_store_kernel(const T* __restrict__ lat, int W, const int*
 // ---------------------------------------------------------------------------
 // qa[m, h, 0:rank] = sum_d q[m, h, d] * uk[h, d, 0:rank];  qa[m, h, rank:] = q[m, h, plain:]
 // uk: [heads * plain, rank] (row (h, d)).  Grid (token tiles of TM, heads), 128 threads over the rank.
-constexpr int ABS_TM = 8, ABS_THREADS = 128, ABS_RPT = 8;      // rank up to 128 * 8
+constexpr int ABS_TM = 8, ABS_THREADS = 128, ABS_RPT = 2;      // a block: 8 tokens, one head, 256 elements of the latent (grid.z)
 
 template <typename T>
 __global__ void __launch_bounds__(ABS_THREADS)
@@ -133,19 +133,21 @@ latent_absorb_kernel(const T* __restrict__ q, long long q_stride, const T* __res
         const int mm = idx / plain, dd = idx - mm * plain;
         qs[idx] = (m0 + mm < M) ? to_f32(q[(size_t)(m0 + mm) * q_stride + (size_t)h * hd + dd]) : 0.f;
     }
-    for (int idx = t; idx < ABS_TM * rot; idx += ABS_THREADS) {
+    for (int idx = t; idx < ABS_TM * rot && blockIdx.z == 0; idx += ABS_THREADS) {
         const int mm = idx / rot, dd = idx - mm * rot;
         if (m0 + mm < M)
             qa[((size_t)(m0 + mm) * n_heads + h) * W + rank + dd] = to_f32(q[(size_t)(m0 + mm) * q_stride + (size_t)h * hd + plain + dd]);
     }
     __syncthreads();
     const T* ukh = uk + (size_t)h * plain * rank;
-    for (int r0 = 0; r0 < rank; r0 += ABS_THREADS * ABS_RPT) {
+    {
+        const int r0 = blockIdx.z * ABS_THREADS * ABS_RPT;
         float acc[ABS_RPT][ABS_TM];
 #pragma unroll
         for (int j = 0; j < ABS_RPT; j++)
 #pragma unroll
             for (int mm = 0; mm < ABS_TM; mm++) acc[j][mm] = 0.f;
+#pragma unroll 4
         for (int dd = 0; dd < plain; dd++) {
             float wv[ABS_RPT];
 #pragma unroll
@@ -173,7 +175,7 @@ latent_absorb_kernel(const T* __restrict__ q, long long q_stride, const T* __res
 
 // o[m, h, v] = sum_r uv[h, v, r] * ol[m, h, r].  uv: [heads * vdim, rank].  Grid (token tiles, heads);
 // a warp per output element row v, lanes along the rank.
-constexpr int EXP_TM = 8, EXP_THREADS = 128;
+constexpr int EXP_TM = 8, EXP_THREADS = 128, EXP_VB = 16;      // a block: 8 tokens, one head, 16 output elements (grid.z)
 
 template <typename T>
 __global__ void __launch_bounds__(EXP_THREADS)
@@ -190,7 +192,8 @@ latent_expand_kernel(const float* __restrict__ ol, const T* __restrict__ uv, T* 
     }
     __syncthreads();
     const int warp = t >> 5, lane = t & 31;
-    for (int v = warp; v < vdim; v += EXP_THREADS / 32) {
+    const int v_end = min(vdim, (int)(blockIdx.z + 1) * EXP_VB);
+    for (int v = blockIdx.z * EXP_VB + warp; v < v_end; v += EXP_THREADS / 32) {
         const T* wrow = uv + ((size_t)h * vdim + v) * rank;
         float acc[EXP_TM];
 #pragma unroll
@@ -370,6 +373,210 @@ latent_attn_kernel(const float* __restrict__ qa, const T* __restrict__ lat, floa
     }
 }
 
+// ---------------------------------------------------------------------------
+// One query per sequence, bfloat16, on the tensor cores (`mma.sync m16n8k16`, float32 accumulation).  A block takes one
+// sequence, 16 * MT heads and one share of the keys, 32 positions at a time: the rows [c | r] of a tile go to shared memory
+// as they are; S = Qa L^T (a warp per 8 keys), the softmax of a row by one thread in 32-bit, P rounded to bfloat16 as the
+// second product's operand, O += P L[:, :rank] (the latent's columns shared out over the warps, a key pair per register
+// fetched as two 16-bit loads).  Unnormalised sums, maxima and denominators go to the merging kernel when the keys are split.
+// Rows of a tile outside the query's reach are zeroed: a weight of zero times whatever stood there must stay zero.
+constexpr int DK = 32, D_THREADS = 128;
+
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+template <int MT, int NTW>
+__global__ void __launch_bounds__(D_THREADS)
+latent_decode_mma_kernel(const float* __restrict__ qa, const bf16* __restrict__ lat, float* __restrict__ ol,
+                         const int* __restrict__ cu_new, const int* __restrict__ seq_start, const int* __restrict__ seq_slot,
+                         int n_heads, int rank, int rot, float scale, int window, const float* __restrict__ sink,
+                         LatentPages kv, int n_splits, float* __restrict__ part_o, float* __restrict__ part_ml) {
+    ti_pdl_trigger();
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    ti_pdl_sync();
+    qa = ti_dependent(qa); lat = ti_dependent(lat);
+    constexpr int ROWS = 16 * MT;
+    const int W = rank + rot, LD = W + 8;
+    bf16* Qs = reinterpret_cast<bf16*>(smem_raw);                  // [ROWS][LD]
+    bf16* Ls = Qs + ROWS * LD;                                     // [DK][LD]
+    bf16* Ps = Ls + DK * LD;                                       // [ROWS][DK + 8]
+    float* Ss = reinterpret_cast<float*>(Ps + ROWS * (DK + 8));    // [ROWS][DK + 1]
+    float* m_s = Ss + ROWS * (DK + 1);                             // [ROWS] running maximum
+    float* l_s = m_s + ROWS;                                       // [ROWS] running denominator
+    float* a_s = l_s + ROWS;                                       // [ROWS] this tile's rescaling
+    const int split = blockIdx.x, h0 = blockIdx.y * ROWS, b = blockIdx.z;
+    const int tok = cu_new[b];
+    if (cu_new[b + 1] - tok <= 0) return;
+    const int qi = seq_start[b], slot = seq_slot[b];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t4 = lane & 3;
+    for (int idx = tid; idx < ROWS * W; idx += D_THREADS) {
+        const int r = idx / W, e = idx - r * W;
+        Qs[r * LD + e] = from_f32<bf16>(h0 + r < n_heads ? qa[((size_t)tok * n_heads + h0 + r) * W + e] : 0.f);
+    }
+    if (tid < ROWS) {
+        const bool with_sink = sink && split == 0 && h0 + tid < n_heads;
+        m_s[tid] = with_sink ? sink[h0 + tid] : -INFINITY;
+        l_s[tid] = with_sink ? 1.f : 0.f;
+    }
+    float O[MT][NTW][4];
+#pragma unroll
+    for (int mt = 0; mt < MT; mt++)
+#pragma unroll
+        for (int i = 0; i < NTW; i++)
+#pragma unroll
+            for (int c = 0; c < 4; c++) O[mt][i][c] = 0.f;
+    const int lo = window > 0 ? max(0, qi - window + 1) : 0;
+    const int kt_first = lo / DK, kt_last = qi / DK;
+    const int per = (kt_last - kt_first + n_splits) / n_splits;
+    const int kt_a = kt_first + split * per, kt_b = min(kt_last, kt_a + per - 1);
+    const int n_tiles8 = rank >> 3;
+    for (int kt = kt_a; kt <= kt_b; kt++) {
+        const int k0 = kt * DK;
+        __syncthreads();
+        for (int rr = warp; rr < DK; rr += D_THREADS / 32) {
+            const int p = k0 + rr;
+            const bf16* src = nullptr;
+            if (p == qi) {
+                src = lat + (size_t)tok * W;
+            } else if (p >= lo && p < qi) {
+                const int row = kv.ring_rows > 0 ? p % kv.ring_rows : p;
+                const int pidx = row / kv.page_size;
+                const int page = pidx < kv.table_width ? kv.page_table[(size_t)slot * kv.table_width + pidx] : -1;
+                if (page >= 0 && page < kv.n_pages) src = (const bf16*)kv.pages + ((size_t)page * kv.page_size + row % kv.page_size) * W;
+            }
+            uint4* dst = reinterpret_cast<uint4*>(Ls + rr * LD);
+            for (int e = lane; e < W / 8; e += 32) dst[e] = src ? reinterpret_cast<const uint4*>(src)[e] : make_uint4(0u, 0u, 0u, 0u);
+        }
+        __syncthreads();
+        // scores: this warp's 8 keys against all rows
+#pragma unroll
+        for (int mt = 0; mt < MT; mt++) {
+            float c[4] = {0.f, 0.f, 0.f, 0.f};
+            const bf16* qrow = Qs + (mt * 16 + g) * LD + 2 * t4;
+            const bf16* krow = Ls + (warp * 8 + g) * LD + 2 * t4;
+            for (int kk = 0; kk < W; kk += 16) {
+                uint32_t a[4];
+                a[0] = *reinterpret_cast<const uint32_t*>(qrow + kk);
+                a[1] = *reinterpret_cast<const uint32_t*>(qrow + 8 * LD + kk);
+                a[2] = *reinterpret_cast<const uint32_t*>(qrow + kk + 8);
+                a[3] = *reinterpret_cast<const uint32_t*>(qrow + 8 * LD + kk + 8);
+                mma_bf16_16816(c, a, *reinterpret_cast<const uint32_t*>(krow + kk), *reinterpret_cast<const uint32_t*>(krow + kk + 8));
+            }
+            float* srow = Ss + (mt * 16 + g) * (DK + 1) + warp * 8 + 2 * t4;
+            srow[0] = c[0]; srow[1] = c[1];
+            srow[8 * (DK + 1)] = c[2]; srow[8 * (DK + 1) + 1] = c[3];
+        }
+        __syncthreads();
+        if (tid < ROWS) {
+            const float* srow = Ss + tid * (DK + 1);
+            const bool head_ok = h0 + tid < n_heads;
+            float mx = -INFINITY;
+            for (int j = 0; j < DK; j++) {
+                const int p = k0 + j;
+                if (head_ok && p >= lo && p <= qi) mx = fmaxf(mx, srow[j] * scale);
+            }
+            const float m_old = m_s[tid], m_new = fmaxf(m_old, mx);
+            const float alpha = m_new > -INFINITY ? expf(m_old - m_new) : 1.f;
+            float sum = 0.f;
+            for (int j = 0; j < DK; j++) {
+                const int p = k0 + j;
+                float pr = 0.f;
+                if (head_ok && p >= lo && p <= qi) pr = expf(srow[j] * scale - m_new);
+                sum += pr;
+                Ps[tid * (DK + 8) + j] = from_f32<bf16>(pr);
+            }
+            m_s[tid] = m_new;
+            l_s[tid] = l_s[tid] * alpha + sum;
+            a_s[tid] = alpha;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int mt = 0; mt < MT; mt++) {
+            const float al0 = a_s[mt * 16 + g], al1 = a_s[mt * 16 + g + 8];
+            uint32_t a[2][4];
+#pragma unroll
+            for (int ks = 0; ks < 2; ks++) {
+                const bf16* prow = Ps + (mt * 16 + g) * (DK + 8) + ks * 16 + 2 * t4;
+                a[ks][0] = *reinterpret_cast<const uint32_t*>(prow);
+                a[ks][1] = *reinterpret_cast<const uint32_t*>(prow + 8 * (DK + 8));
+                a[ks][2] = *reinterpret_cast<const uint32_t*>(prow + 8);
+                a[ks][3] = *reinterpret_cast<const uint32_t*>(prow + 8 * (DK + 8) + 8);
+            }
+#pragma unroll
+            for (int i = 0; i < NTW; i++) {
+                const int nt = warp + 4 * i;
+                if (nt >= n_tiles8) continue;
+                O[mt][i][0] *= al0; O[mt][i][1] *= al0; O[mt][i][2] *= al1; O[mt][i][3] *= al1;
+                const unsigned short* col = reinterpret_cast<const unsigned short*>(Ls) + nt * 8 + g;
+#pragma unroll
+                for (int ks = 0; ks < 2; ks++) {
+                    const int kr = ks * 16 + 2 * t4;
+                    const uint32_t b0 = (uint32_t)col[(size_t)kr * LD] | ((uint32_t)col[(size_t)(kr + 1) * LD] << 16);
+                    const uint32_t b1 = (uint32_t)col[(size_t)(kr + 8) * LD] | ((uint32_t)col[(size_t)(kr + 9) * LD] << 16);
+                    mma_bf16_16816(O[mt][i], a[ks], b0, b1);
+                }
+            }
+        }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int mt = 0; mt < MT; mt++)
+#pragma unroll
+        for (int half = 0; half < 2; half++) {
+            const int r = mt * 16 + g + 8 * half, h = h0 + r;
+            if (h >= n_heads) continue;
+            const float l = l_s[r];
+            if (n_splits > 1) {
+                const size_t at = ((size_t)tok * n_heads + h) * n_splits + split;
+                if (t4 == 0 && warp == 0) { part_ml[at * 2] = m_s[r]; part_ml[at * 2 + 1] = l; }
+#pragma unroll
+                for (int i = 0; i < NTW; i++) {
+                    const int nt = warp + 4 * i;
+                    if (nt >= n_tiles8) continue;
+                    float* dst = part_o + at * rank + nt * 8 + 2 * t4;
+                    dst[0] = O[mt][i][2 * half]; dst[1] = O[mt][i][2 * half + 1];
+                }
+            } else {
+                const float inv = l > 0.f ? 1.f / l : 0.f;
+#pragma unroll
+                for (int i = 0; i < NTW; i++) {
+                    const int nt = warp + 4 * i;
+                    if (nt >= n_tiles8) continue;
+                    float* dst = ol + ((size_t)tok * n_heads + h) * rank + nt * 8 + 2 * t4;
+                    dst[0] = O[mt][i][2 * half] * inv; dst[1] = O[mt][i][2 * half + 1] * inv;
+                }
+            }
+        }
+}
+
+template <int MT, int NTW>
+int launch_decode_mma(const float* qa, const void* lat, float* ol, const int* cu_new, const int* seq_start, const int* seq_slot,
+                      int n_seq, int n_heads, int rank, int rot, float scale, int window, const float* sink,
+                      const LatentPages& kv, int n_splits, float* part_o, float* part_ml, int n_tok, cudaStream_t stream) {
+    constexpr int ROWS = 16 * MT;
+    const int W = rank + rot, LD = W + 8;
+    const size_t smem = (size_t)(ROWS + DK) * LD * 2 + (size_t)ROWS * (DK + 8) * 2 + ((size_t)ROWS * (DK + 1) + 3 * ROWS) * 4;
+    static size_t configured = 0;
+    if (smem > 48 * 1024 && smem > configured) {
+        TI_CUDA(cudaFuncSetAttribute(latent_decode_mma_kernel<MT, NTW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        configured = smem;
+    }
+    dim3 grid(n_splits, (n_heads + ROWS - 1) / ROWS, n_seq);
+    TI_CUDA(ti_launch_class<3>(latent_decode_mma_kernel<MT, NTW>, grid, dim3(D_THREADS), smem, stream, qa, (const bf16*)lat, ol, cu_new,
+                               seq_start, seq_slot, n_heads, rank, rot, scale, window, sink, kv, n_splits, part_o, part_ml));
+    TI_CHECK_LAUNCH("latent_attention (one token, tensor cores)");
+    if (n_splits > 1) {
+        int threads = ((rank + 3) / 4 + 31) / 32 * 32;
+        TI_CUDA(ti_launch_class<4>(tiattn::attn_decode_combine_kernel<float>, dim3(n_tok, n_heads), dim3(threads), 0, stream,
+                                   (const float*)part_o, (const float*)part_ml, ol, (long long)n_heads * rank, n_heads, rank, n_splits));
+        TI_CHECK_LAUNCH("latent_attention_combine");
+    }
+    return 0;
+}
+
 template <typename T, int MAXC>
 int launch_attn(const float* qa, const void* lat, float* ol, const int* cu_new, const int* seq_start, const int* seq_slot,
                 int n_seq, int max_new, int n_heads, int hb, int rank, int rot, float scale, int window, const float* sink,
@@ -463,7 +670,8 @@ extern "C" int ti_latent_absorb(const void* q, long long q_stride, const void* u
     TI_REQUIRE(smem <= 48 * 1024, "latent_absorb: heads of %d unrotated elements are too long", plain);
     return ti_dispatch_dtype(dtype, [&](auto t) -> int {
         using T = decltype(t);
-        TI_CUDA(ti_launch(latent_absorb_kernel<T>, dim3((M + ABS_TM - 1) / ABS_TM, n_heads), dim3(ABS_THREADS), smem, stream,
+        const int zs = (rank + ABS_THREADS * ABS_RPT - 1) / (ABS_THREADS * ABS_RPT);
+        TI_CUDA(ti_launch(latent_absorb_kernel<T>, dim3((M + ABS_TM - 1) / ABS_TM, n_heads, zs), dim3(ABS_THREADS), smem, stream,
                           (const T*)q, q_stride, (const T*)uk, qa, M, n_heads, plain, rank, rot));
         TI_CHECK_LAUNCH("latent_absorb");
         return 0;
@@ -478,7 +686,7 @@ extern "C" int ti_latent_expand(const float* ol, const void* uv, void* o, long l
     TI_REQUIRE(smem <= 48 * 1024, "latent_expand: a latent of %d elements is too long", rank);
     return ti_dispatch_dtype(dtype, [&](auto t) -> int {
         using T = decltype(t);
-        TI_CUDA(ti_launch(latent_expand_kernel<T>, dim3((M + EXP_TM - 1) / EXP_TM, n_heads), dim3(EXP_THREADS), smem, stream, ol,
+        TI_CUDA(ti_launch(latent_expand_kernel<T>, dim3((M + EXP_TM - 1) / EXP_TM, n_heads, (vdim + EXP_VB - 1) / EXP_VB), dim3(EXP_THREADS), smem, stream, ol,
                           (const T*)uv, (T*)o, o_stride, M, n_heads, vdim, rank));
         TI_CHECK_LAUNCH("latent_expand");
         return 0;
@@ -504,6 +712,17 @@ extern "C" int ti_latent_attn(const float* qa, const void* lat, float* ol, const
     TI_REQUIRE(n_splits >= 1 && (n_splits == 1 || (part_o && part_ml && n_tok > 0 && n_tok <= 65535 * 32768)),
                "latent_attention: %d splits need room for their partial results", n_splits);
     LatentPages kv{const_cast<void*>(pages), page_table, table_width, page_size, ring_rows, n_pages, nullptr};
+    // every sequence brings one token, bfloat16, rows in 16-byte pieces: the tensor-core kernel
+    if (dtype == TI_BF16 && max_new == 1 && n_tok == n_seq && (rank + rot) % 16 == 0 && rank % 8 == 0 && rank <= 512 &&
+        ((uintptr_t)lat & 15) == 0 && ((uintptr_t)pages & 15) == 0) {
+        const bool two = n_heads > 16;
+#define TI_LATENT_DECODE(MT, NTW) launch_decode_mma<MT, NTW>(qa, lat, ol, cu_new, seq_start, seq_slot, n_seq, n_heads, rank, rot, scale, \
+                                                            window, sink, kv, n_splits, part_o, part_ml, n_tok, stream)
+        if (rank <= 128) return two ? TI_LATENT_DECODE(2, 4) : TI_LATENT_DECODE(1, 4);
+        if (rank <= 256) return two ? TI_LATENT_DECODE(2, 8) : TI_LATENT_DECODE(1, 8);
+        return two ? TI_LATENT_DECODE(2, 16) : TI_LATENT_DECODE(1, 16);
+#undef TI_LATENT_DECODE
+    }
     return ti_dispatch_dtype(dtype, [&](auto t) -> int {
         using T = decltype(t);
         if (rank <= 64)

@@ -110,42 +110,70 @@ __device__ __forceinline__ bool find_chunk(const Chunks& cz, int chunk, int& b, 
     return false;
 }
 
-// (1) U[chunk, h] = sum_s lam^(len-1-s) k_s v_s^T over the chunk's tokens; thread owns a column.
-template <typename T, int MAXD>
-__global__ void lightning_chunk_local_kernel(const T* __restrict__ k, const T* __restrict__ v, long long k_stride,
-                                             long long v_stride, float* __restrict__ U, const float* __restrict__ decay,
-                                             Chunks cz, int n_heads, int dim, int vdim, int groups) {
+// The chunk kernels are small matrix products on the CUDA cores in 32-bit, operands in shared memory, a thread a tile of
+// the result in registers.  Column groups of 128: grid.x = heads * groups.
+constexpr int CT = 256;          // threads of a chunk kernel
+constexpr int VG = 128;          // value columns per block
+
+// (1) U[chunk, h][i][j] = sum_s lam^(nt-1-s) k_s[i] v_s[j] over the chunk's nt tokens: a [dim x nt] x [nt x VG] product.
+// Thread (ty, tx) of 16 x 16: rows i = ty + 16 a (a < 8), columns j = 8 tx .. 8 tx + 7.
+template <typename T>
+__global__ void __launch_bounds__(CT)
+lightning_chunk_local_kernel(const T* __restrict__ k, const T* __restrict__ v, long long k_stride, long long v_stride,
+                             float* __restrict__ U, const float* __restrict__ decay, Chunks cz, int n_heads, int dim,
+                             int vdim, int groups) {
     ti_pdl_trigger();
-    extern __shared__ float ks[];        // [CH][dim]
+    extern __shared__ float sm[];
+    float* ks = sm;                      // [CH][128]  (lam^(nt-1-s) k_s, zero past dim)
+    float* vs = ks + CH * 128;           // [CH][VG]
     ti_pdl_sync();
     k = ti_dependent(k); v = ti_dependent(v);
     const int h = blockIdx.x / groups, g = blockIdx.x - h * groups;
     int b, c, tok0, n;
     if (!find_chunk(cz, blockIdx.y, b, c, tok0, n)) return;
-    const int t0 = c * CH, nt = min(CH, n - t0);
-    const int col = g * blockDim.x + threadIdx.x;
-    const bool live = col < vdim;
+    const int t0 = c * CH, nt = min(CH, n - t0), j0 = g * VG;
     const float lam = decay[h];
-    for (int idx = threadIdx.x; idx < nt * dim; idx += blockDim.x) {
-        const int tt = idx / dim, i = idx - tt * dim;
-        ks[idx] = silu_f(to_f32(k[(size_t)(tok0 + t0 + tt) * k_stride + (size_t)h * dim + i]));
+    for (int idx = threadIdx.x; idx < CH * 128; idx += CT) {
+        const int tt = idx >> 7, i = idx & 127;
+        float x = 0.f;
+        if (tt < nt && i < dim) x = silu_f(to_f32(k[(size_t)(tok0 + t0 + tt) * k_stride + (size_t)h * dim + i])) * powf(lam, (float)(nt - 1 - tt));
+        ks[idx] = x;
+    }
+    for (int idx = threadIdx.x; idx < CH * VG; idx += CT) {
+        const int tt = idx >> 7, j = idx & 127;
+        float x = 0.f;
+        if (tt < nt && j0 + j < vdim) x = silu_f(to_f32(v[(size_t)(tok0 + t0 + tt) * v_stride + (size_t)h * vdim + j0 + j]));
+        vs[idx] = x;
     }
     __syncthreads();
-    if (!live) return;
-    float S[MAXD];
+    const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;
+    float acc[8][8];
 #pragma unroll
-    for (int i = 0; i < MAXD; i++) S[i] = 0.f;
+    for (int a = 0; a < 8; a++)
+#pragma unroll
+        for (int e = 0; e < 8; e++) acc[a][e] = 0.f;
     for (int tt = 0; tt < nt; tt++) {
-        const float vv = silu_f(to_f32(v[(size_t)(tok0 + t0 + tt) * v_stride + (size_t)h * vdim + col]));
-        const float* kr = ks + tt * dim;
+        float kv[8], vv[8];
 #pragma unroll
-        for (int i = 0; i < MAXD; i++)
-            if (i < dim) S[i] = fmaf(lam, S[i], kr[i] * vv);
+        for (int a = 0; a < 8; a++) kv[a] = ks[tt * 128 + ty + 16 * a];
+        const float4 v0 = *reinterpret_cast<const float4*>(vs + tt * VG + 8 * tx), v1 = *reinterpret_cast<const float4*>(vs + tt * VG + 8 * tx + 4);
+        vv[0] = v0.x; vv[1] = v0.y; vv[2] = v0.z; vv[3] = v0.w; vv[4] = v1.x; vv[5] = v1.y; vv[6] = v1.z; vv[7] = v1.w;
+#pragma unroll
+        for (int a = 0; a < 8; a++)
+#pragma unroll
+            for (int e = 0; e < 8; e++) acc[a][e] = fmaf(kv[a], vv[e], acc[a][e]);
     }
     float* u = U + ((size_t)blockIdx.y * n_heads + h) * dim * vdim;
 #pragma unroll
-    for (int i = 0; i < MAXD; i++)
-        if (i < dim) u[(size_t)i * vdim + col] = S[i];
+    for (int a = 0; a < 8; a++) {
+        const int i = ty + 16 * a;
+        if (i >= dim) continue;
+#pragma unroll
+        for (int e = 0; e < 8; e++) {
+            const int j = j0 + 8 * tx + e;
+            if (j < vdim) u[(size_t)i * vdim + j] = acc[a][e];
+        }
+    }
 }
 
 // (2) per sequence and head, over its chunks in order: U[chunk] <- state before the chunk, state <- state after the
@@ -163,77 +191,137 @@ __global__ void lightning_chunk_scan_kernel(float* __restrict__ U, float* __rest
     if (n <= 0) return;
     const int nchunks = (n + CH - 1) / CH;
     const float lam = decay[h];
+    const float whole = powf(lam, (float)CH), rest = powf(lam, (float)(n - (nchunks - 1) * CH));
     float* sp = state + ((size_t)cz.seq_slot[b] * n_heads + h) * dim * vdim + e;
+    float* u = U + ((size_t)first * n_heads + h) * dim * vdim + e;
+    const size_t step = (size_t)n_heads * dim * vdim;
     float S = *sp;
+    float own = *u;
     for (int c = 0; c < nchunks; c++) {
-        const int nt = min(CH, n - c * CH);
-        float* u = U + ((size_t)(first + c) * n_heads + h) * dim * vdim + e;
-        const float own = *u;
+        const float next = c + 1 < nchunks ? u[step] : 0.f;      // asked for before this chunk's store
         *u = S;
-        S = fmaf(powf(lam, (float)nt), S, own);
+        S = fmaf(c + 1 < nchunks ? whole : rest, S, own);
+        own = next;
+        u += step;
     }
     *sp = S;
 }
 
-// (3) outputs of a chunk: thread owns an output column (the state's column in registers, the chunk's values of
-// the column in shared memory); A[t][s] = lam^(t-s) (q_t . k_s) for s <= t is formed by the whole block first.
-template <typename T, int MAXD>
-__global__ void lightning_chunk_out_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v,
-                                           long long q_stride, long long k_stride, long long v_stride,
-                                           const float* __restrict__ U, float* __restrict__ o,
-                                           const float* __restrict__ decay, Chunks cz, int n_heads, int dim, int vdim, int groups) {
+// (3) outputs of a chunk, O = diag(lam^(t+1)) Q S + A V with A[t][s] = lam^(t-s) (q_t . k_s) for s <= t, S the state before
+// the chunk: A is formed first (a [nt x dim] x [dim x nt] product), then the two products add into the same registers.
+// Thread (ty, tx) of 16 x 16: tokens t = ty + 16 a (a < 4), columns j = 8 tx .. 8 tx + 7.
+template <typename T>
+__global__ void __launch_bounds__(CT)
+lightning_chunk_out_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v,
+                           long long q_stride, long long k_stride, long long v_stride,
+                           const float* __restrict__ U, float* __restrict__ o,
+                           const float* __restrict__ decay, Chunks cz, int n_heads, int dim, int vdim, int groups) {
     ti_pdl_trigger();
     extern __shared__ float sm[];
     ti_pdl_sync();
     q = ti_dependent(q); k = ti_dependent(k); v = ti_dependent(v); U = ti_dependent(U);
-    const int ldq = dim + 1;
-    float* qs = sm;                      // [CH][dim + 1]
-    float* ks = qs + CH * ldq;           // [CH][dim + 1]
-    float* A = ks + CH * ldq;            // [CH][CH + 1]
+    constexpr int LDQ = 129;
+    float* qs = sm;                      // [CH][129]
+    float* kv = qs + CH * LDQ;           // [CH][129] keys, later [CH][VG] values
+    float* A = kv + CH * LDQ;            // [CH][CH + 1]
     float* pw = A + CH * (CH + 1);       // lam^0 .. lam^CH
-    float* vs = pw + CH + 1;             // [CH][blockDim.x]
+    float* Ss = pw + CH + 4;             // [128][VG] the state before the chunk (zero past dim)
     const int h = blockIdx.x / groups, g = blockIdx.x - h * groups;
     int b, c, tok0, n;
     if (!find_chunk(cz, blockIdx.y, b, c, tok0, n)) return;
-    const int t0 = c * CH, nt = min(CH, n - t0);
+    const int t0 = c * CH, nt = min(CH, n - t0), j0 = g * VG;
     const float lam = decay[h];
-    const int col = g * blockDim.x + threadIdx.x;
-    const bool live = col < vdim;
-    for (int idx = threadIdx.x; idx < nt * dim; idx += blockDim.x) {
-        const int tt = idx / dim, i = idx - tt * dim;
-        const size_t tok = (size_t)(tok0 + t0 + tt);
-        qs[tt * ldq + i] = silu_f(to_f32(q[tok * q_stride + (size_t)h * dim + i]));
-        ks[tt * ldq + i] = silu_f(to_f32(k[tok * k_stride + (size_t)h * dim + i]));
-    }
-    for (int tt = 0; tt < nt; tt++)
-        vs[tt * blockDim.x + threadIdx.x] = live ? silu_f(to_f32(v[(size_t)(tok0 + t0 + tt) * v_stride + (size_t)h * vdim + col])) : 0.f;
-    for (int i = threadIdx.x; i <= CH; i += blockDim.x) pw[i] = powf(lam, (float)i);
-    __syncthreads();
-    for (int idx = threadIdx.x; idx < nt * nt; idx += blockDim.x) {
-        const int tt = idx / nt, ss = idx - tt * nt;
-        float a = 0.f;
-        if (ss <= tt) {
-            for (int i = 0; i < dim; i++) a = fmaf(qs[tt * ldq + i], ks[ss * ldq + i], a);
-            a *= pw[tt - ss];
+    for (int idx = threadIdx.x; idx < CH * 128; idx += CT) {
+        const int tt = idx >> 7, i = idx & 127;
+        float a = 0.f, bb = 0.f;
+        if (tt < nt && i < dim) {
+            const size_t tok = (size_t)(tok0 + t0 + tt);
+            a = silu_f(to_f32(q[tok * q_stride + (size_t)h * dim + i]));
+            bb = silu_f(to_f32(k[tok * k_stride + (size_t)h * dim + i]));
         }
-        A[tt * (CH + 1) + ss] = a;
+        qs[tt * LDQ + i] = a;
+        kv[tt * LDQ + i] = bb;
     }
+    const float* Sg = U + ((size_t)blockIdx.y * n_heads + h) * dim * vdim;
+    for (int idx = threadIdx.x; idx < 128 * VG; idx += CT) {
+        const int i = idx >> 7, j = idx & 127;
+        Ss[idx] = (i < dim && j0 + j < vdim) ? Sg[(size_t)i * vdim + j0 + j] : 0.f;
+    }
+    for (int i = threadIdx.x; i <= CH; i += CT) pw[i] = powf(lam, (float)i);
     __syncthreads();
-    if (!live) return;
-    const float* Sg = U + ((size_t)blockIdx.y * n_heads + h) * dim * vdim;      // the state before this chunk
-    float S[MAXD];
+    const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;
+    {   // A: tokens t = ty + 16 a, keys s = tx + 16 e (a, e < 4)
+        float acc[4][4];
 #pragma unroll
-    for (int i = 0; i < MAXD; i++) S[i] = i < dim ? Sg[(size_t)i * vdim + col] : 0.f;
-    for (int tt = 0; tt < nt; tt++) {
-        float acc = 0.f;
-        const float* qr = qs + tt * ldq;
+        for (int a = 0; a < 4; a++)
 #pragma unroll
-        for (int i = 0; i < MAXD; i++)
-            if (i < dim) acc = fmaf(S[i], qr[i], acc);
-        acc *= pw[tt + 1];
-        const float* arow = A + tt * (CH + 1);
-        for (int ss = 0; ss <= tt; ss++) acc = fmaf(arow[ss], vs[ss * blockDim.x + threadIdx.x], acc);
-        o[(size_t)(tok0 + t0 + tt) * ((size_t)n_heads * vdim) + (size_t)h * vdim + col] = acc;
+            for (int e = 0; e < 4; e++) acc[a][e] = 0.f;
+        for (int i = 0; i < dim; i++) {
+            float qv[4], kk[4];
+#pragma unroll
+            for (int a = 0; a < 4; a++) { qv[a] = qs[(ty + 16 * a) * LDQ + i]; kk[a] = kv[(tx + 16 * a) * LDQ + i]; }
+#pragma unroll
+            for (int a = 0; a < 4; a++)
+#pragma unroll
+                for (int e = 0; e < 4; e++) acc[a][e] = fmaf(qv[a], kk[e], acc[a][e]);
+        }
+#pragma unroll
+        for (int a = 0; a < 4; a++)
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                const int tt = ty + 16 * a, ss = tx + 16 * e;
+                A[tt * (CH + 1) + ss] = (ss <= tt && tt < nt) ? acc[a][e] * pw[tt - ss] : 0.f;
+            }
+    }
+    __syncthreads();                     // A is whole, the keys are done with
+    for (int idx = threadIdx.x; idx < CH * VG; idx += CT) {
+        const int tt = idx >> 7, j = idx & 127;
+        float x = 0.f;
+        if (tt < nt && j0 + j < vdim) x = silu_f(to_f32(v[(size_t)(tok0 + t0 + tt) * v_stride + (size_t)h * vdim + j0 + j]));
+        kv[idx] = x;
+    }
+    float acc[4][8];
+#pragma unroll
+    for (int a = 0; a < 4; a++)
+#pragma unroll
+        for (int e = 0; e < 8; e++) acc[a][e] = 0.f;
+    for (int i = 0; i < dim; i++) {
+        float qv[4], sv[8];
+#pragma unroll
+        for (int a = 0; a < 4; a++) qv[a] = qs[(ty + 16 * a) * LDQ + i];
+        const float4 s0 = *reinterpret_cast<const float4*>(Ss + i * VG + 8 * tx), s1 = *reinterpret_cast<const float4*>(Ss + i * VG + 8 * tx + 4);
+        sv[0] = s0.x; sv[1] = s0.y; sv[2] = s0.z; sv[3] = s0.w; sv[4] = s1.x; sv[5] = s1.y; sv[6] = s1.z; sv[7] = s1.w;
+#pragma unroll
+        for (int a = 0; a < 4; a++)
+#pragma unroll
+            for (int e = 0; e < 8; e++) acc[a][e] = fmaf(qv[a], sv[e], acc[a][e]);
+    }
+#pragma unroll
+    for (int a = 0; a < 4; a++)
+#pragma unroll
+        for (int e = 0; e < 8; e++) acc[a][e] *= pw[ty + 16 * a + 1];
+    __syncthreads();                     // the values are in place
+    for (int ss = 0; ss < nt; ss++) {
+        float av[4], vv[8];
+#pragma unroll
+        for (int a = 0; a < 4; a++) av[a] = A[(ty + 16 * a) * (CH + 1) + ss];
+        const float4 v0 = *reinterpret_cast<const float4*>(kv + ss * VG + 8 * tx), v1 = *reinterpret_cast<const float4*>(kv + ss * VG + 8 * tx + 4);
+        vv[0] = v0.x; vv[1] = v0.y; vv[2] = v0.z; vv[3] = v0.w; vv[4] = v1.x; vv[5] = v1.y; vv[6] = v1.z; vv[7] = v1.w;
+#pragma unroll
+        for (int a = 0; a < 4; a++)
+#pragma unroll
+            for (int e = 0; e < 8; e++) acc[a][e] = fmaf(av[a], vv[e], acc[a][e]);
+    }
+#pragma unroll
+    for (int a = 0; a < 4; a++) {
+        const int tt = ty + 16 * a;
+        if (tt >= nt) continue;
+        float* orow = o + (size_t)(tok0 + t0 + tt) * ((size_t)n_heads * vdim) + (size_t)h * vdim;
+#pragma unroll
+        for (int e = 0; e < 8; e++) {
+            const int j = j0 + 8 * tx + e;
+            if (j < vdim) orow[j] = acc[a][e];
+        }
     }
 }
 
@@ -301,31 +389,30 @@ extern "C" int ti_lightning_chunked(const void* q, const void* k, const void* v,
     if (n_seq == 0 || n_chunks == 0) return 0;
     TI_REQUIRE(n_seq > 0 && n_seq <= 65535 && n_chunks > 0 && n_chunks <= 65535 && n_heads > 0 && n_heads <= 65535 && dim > 0 && vdim > 0,
                "lightning_chunked: bad sizes");
-    const int threads = column_threads(vdim), groups = (vdim + threads - 1) / threads;
+    TI_REQUIRE(dim <= 128, "lightning: heads of %d query/key elements are not supported (up to 128)", dim);
+    const int groups = (vdim + VG - 1) / VG;
     Chunks cz{cu_new, seq_slot, n_seq};
     return ti_dispatch_dtype(dtype, [&](auto t) -> int {
         using T = decltype(t);
-        return dispatch_dim(dim, [&](auto md) -> int {
-            constexpr int MAXD = decltype(md)::value;
-            const size_t smem1 = (size_t)CH * dim * sizeof(float);
-            TI_CUDA(ti_launch(lightning_chunk_local_kernel<T, MAXD>, dim3(n_heads * groups, n_chunks), dim3(threads), smem1, stream,
-                              (const T*)k, (const T*)v, k_stride, v_stride, U, decay, cz, n_heads, dim, vdim, groups));
-            TI_CHECK_LAUNCH("lightning_chunk_local");
-            TI_CUDA(ti_launch(lightning_chunk_scan_kernel, dim3((dim * vdim + 127) / 128, n_heads, n_seq), dim3(128), 0, stream,
-                              U, state, decay, cz, n_heads, dim, vdim));
-            TI_CHECK_LAUNCH("lightning_chunk_scan");
-            const size_t smem3 = ((size_t)2 * CH * (dim + 1) + (size_t)CH * (CH + 1) + CH + 1 + (size_t)CH * threads) * sizeof(float);
-            static size_t configured = 0;
-            if (smem3 > 48 * 1024 && smem3 > configured) {
-                TI_CUDA(cudaFuncSetAttribute(lightning_chunk_out_kernel<T, MAXD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem3));
-                configured = smem3;
-            }
-            TI_CUDA(ti_launch(lightning_chunk_out_kernel<T, MAXD>, dim3(n_heads * groups, n_chunks), dim3(threads), smem3, stream,
-                              (const T*)q, (const T*)k, (const T*)v, q_stride, k_stride, v_stride, (const float*)U, o, decay, cz,
-                              n_heads, dim, vdim, groups));
-            TI_CHECK_LAUNCH("lightning_chunk_out");
-            return 0;
-        });
+        const size_t smem1 = (size_t)(CH * 128 + CH * VG) * sizeof(float);
+        const size_t smem3 = ((size_t)2 * CH * 129 + (size_t)CH * (CH + 1) + CH + 4 + (size_t)128 * VG) * sizeof(float);
+        static bool configured = false;
+        if (!configured) {
+            TI_CUDA(cudaFuncSetAttribute(lightning_chunk_local_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem1));
+            TI_CUDA(cudaFuncSetAttribute(lightning_chunk_out_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem3));
+            configured = true;
+        }
+        TI_CUDA(ti_launch(lightning_chunk_local_kernel<T>, dim3(n_heads * groups, n_chunks), dim3(CT), smem1, stream,
+                          (const T*)k, (const T*)v, k_stride, v_stride, U, decay, cz, n_heads, dim, vdim, groups));
+        TI_CHECK_LAUNCH("lightning_chunk_local");
+        TI_CUDA(ti_launch(lightning_chunk_scan_kernel, dim3((dim * vdim + 127) / 128, n_heads, n_seq), dim3(128), 0, stream,
+                          U, state, decay, cz, n_heads, dim, vdim));
+        TI_CHECK_LAUNCH("lightning_chunk_scan");
+        TI_CUDA(ti_launch(lightning_chunk_out_kernel<T>, dim3(n_heads * groups, n_chunks), dim3(CT), smem3, stream,
+                          (const T*)q, (const T*)k, (const T*)v, q_stride, k_stride, v_stride, (const float*)U, o, decay, cz,
+                          n_heads, dim, vdim, groups));
+        TI_CHECK_LAUNCH("lightning_chunk_out");
+        return 0;
     });
 }
 

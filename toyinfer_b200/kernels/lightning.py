@@ -11,7 +11,7 @@ from .wide import _fn
 
 P, I, L, F = c_void_p, c_int, c_longlong, c_float
 CHUNK = 64                 # tokens per chunk of the chunked form (csrc/lightning.cu)
-CHUNKED_FROM = 192         # new tokens of one sequence from which a step runs the chunked form
+CHUNKED_FROM = 32          # new tokens of one sequence from which a step runs the chunked form (three launches)
 
 
 def mix(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, state: torch.Tensor, decay: torch.Tensor, batch) -> torch.Tensor:
