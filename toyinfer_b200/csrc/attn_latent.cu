@@ -407,14 +407,32 @@ latent_decode_mma_kernel(const float* __restrict__ qa, const bf16* __restrict__ 
     float* m_s = Ss + ROWS * (DK + 1);                             // [ROWS] running maximum
     float* l_s = m_s + ROWS;                                       // [ROWS] running denominator
     float* a_s = l_s + ROWS;                                       // [ROWS] this tile's rescaling
+    __shared__ const bf16* row_src[DK];
     const int split = blockIdx.x, h0 = blockIdx.y * ROWS, b = blockIdx.z;
     const int tok = cu_new[b];
     if (cu_new[b + 1] - tok <= 0) return;
     const int qi = seq_start[b], slot = seq_slot[b];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t4 = lane & 3;
-    for (int idx = tid; idx < ROWS * W; idx += D_THREADS) {
-        const int r = idx / W, e = idx - r * W;
-        Qs[r * LD + e] = from_f32<bf16>(h0 + r < n_heads ? qa[((size_t)tok * n_heads + h0 + r) * W + e] : 0.f);
+    // (global loads in batches, so that several are on their way at a time: a block's four warps cannot hide one each)
+    {
+        const int per_row = W >> 2, total = ROWS * per_row;        // pieces of four floats
+        for (int i0 = 0; i0 < total; i0 += 6 * D_THREADS) {
+            float4 x[6];
+#pragma unroll
+            for (int u = 0; u < 6; u++) {
+                const int idx = i0 + u * D_THREADS + tid, r = idx / per_row, e = idx - r * per_row;
+                x[u] = (idx < total && h0 + r < n_heads) ? reinterpret_cast<const float4*>(qa + ((size_t)tok * n_heads + h0 + r) * W)[e]
+                                                         : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int u = 0; u < 6; u++) {
+                const int idx = i0 + u * D_THREADS + tid, r = idx / per_row, e = idx - r * per_row;
+                if (idx < total) {
+                    bf16* dst = Qs + r * LD + 4 * e;
+                    dst[0] = from_f32<bf16>(x[u].x); dst[1] = from_f32<bf16>(x[u].y); dst[2] = from_f32<bf16>(x[u].z); dst[3] = from_f32<bf16>(x[u].w);
+                }
+            }
+        }
     }
     if (tid < ROWS) {
         const bool with_sink = sink && split == 0 && h0 + tid < n_heads;
@@ -436,8 +454,8 @@ latent_decode_mma_kernel(const float* __restrict__ qa, const bf16* __restrict__ 
     for (int kt = kt_a; kt <= kt_b; kt++) {
         const int k0 = kt * DK;
         __syncthreads();
-        for (int rr = warp; rr < DK; rr += D_THREADS / 32) {
-            const int p = k0 + rr;
+        if (tid < DK) {              // where each of the tile's rows lives
+            const int p = k0 + tid;
             const bf16* src = nullptr;
             if (p == qi) {
                 src = lat + (size_t)tok * W;
@@ -447,8 +465,25 @@ latent_decode_mma_kernel(const float* __restrict__ qa, const bf16* __restrict__ 
                 const int page = pidx < kv.table_width ? kv.page_table[(size_t)slot * kv.table_width + pidx] : -1;
                 if (page >= 0 && page < kv.n_pages) src = (const bf16*)kv.pages + ((size_t)page * kv.page_size + row % kv.page_size) * W;
             }
-            uint4* dst = reinterpret_cast<uint4*>(Ls + rr * LD);
-            for (int e = lane; e < W / 8; e += 32) dst[e] = src ? reinterpret_cast<const uint4*>(src)[e] : make_uint4(0u, 0u, 0u, 0u);
+            row_src[tid] = src;
+        }
+        __syncthreads();
+        {
+            const int per_row = W >> 3, total = DK * per_row;          // 16-byte pieces
+            for (int i0 = 0; i0 < total; i0 += 6 * D_THREADS) {
+                uint4 x[6];
+#pragma unroll
+                for (int u = 0; u < 6; u++) {
+                    const int idx = i0 + u * D_THREADS + tid, rr = idx / per_row, e = idx - rr * per_row;
+                    const bf16* src = idx < total ? row_src[rr] : nullptr;
+                    x[u] = src ? reinterpret_cast<const uint4*>(src)[e] : make_uint4(0u, 0u, 0u, 0u);
+                }
+#pragma unroll
+                for (int u = 0; u < 6; u++) {
+                    const int idx = i0 + u * D_THREADS + tid, rr = idx / per_row, e = idx - rr * per_row;
+                    if (idx < total) reinterpret_cast<uint4*>(Ls + rr * LD)[e] = x[u];
+                }
+            }
         }
         __syncthreads();
         // scores: this warp's 8 keys against all rows

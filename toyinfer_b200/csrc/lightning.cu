@@ -133,17 +133,21 @@ lightning_chunk_local_kernel(const T* __restrict__ k, const T* __restrict__ v, l
     if (!find_chunk(cz, blockIdx.y, b, c, tok0, n)) return;
     const int t0 = c * CH, nt = min(CH, n - t0), j0 = g * VG;
     const float lam = decay[h];
-    for (int idx = threadIdx.x; idx < CH * 128; idx += CT) {
-        const int tt = idx >> 7, i = idx & 127;
-        float x = 0.f;
-        if (tt < nt && i < dim) x = silu_f(to_f32(k[(size_t)(tok0 + t0 + tt) * k_stride + (size_t)h * dim + i])) * powf(lam, (float)(nt - 1 - tt));
-        ks[idx] = x;
-    }
-    for (int idx = threadIdx.x; idx < CH * VG; idx += CT) {
-        const int tt = idx >> 7, j = idx & 127;
-        float x = 0.f;
-        if (tt < nt && j0 + j < vdim) x = silu_f(to_f32(v[(size_t)(tok0 + t0 + tt) * v_stride + (size_t)h * vdim + j0 + j]));
-        vs[idx] = x;
+    // (loads in batches of 8, so that eight are on their way at a time: a block's few warps cannot hide one load each)
+    for (int it = 0; it < CH * 128 / CT; it += 8) {
+        float x[8], y[8];
+#pragma unroll
+        for (int u = 0; u < 8; u++) {
+            const int idx = (it + u) * CT + threadIdx.x, tt = idx >> 7, i = idx & 127;
+            x[u] = (tt < nt && i < dim) ? to_f32(k[(size_t)(tok0 + t0 + tt) * k_stride + (size_t)h * dim + i]) : 0.f;
+            y[u] = (tt < nt && j0 + i < vdim) ? to_f32(v[(size_t)(tok0 + t0 + tt) * v_stride + (size_t)h * vdim + j0 + i]) : 0.f;
+        }
+#pragma unroll
+        for (int u = 0; u < 8; u++) {
+            const int idx = (it + u) * CT + threadIdx.x, tt = idx >> 7, i = idx & 127;
+            ks[idx] = (tt < nt && i < dim) ? silu_f(x[u]) * powf(lam, (float)(nt - 1 - tt)) : 0.f;
+            vs[idx] = (tt < nt && j0 + i < vdim) ? silu_f(y[u]) : 0.f;
+        }
     }
     __syncthreads();
     const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;
@@ -231,21 +235,35 @@ lightning_chunk_out_kernel(const T* __restrict__ q, const T* __restrict__ k, con
     if (!find_chunk(cz, blockIdx.y, b, c, tok0, n)) return;
     const int t0 = c * CH, nt = min(CH, n - t0), j0 = g * VG;
     const float lam = decay[h];
-    for (int idx = threadIdx.x; idx < CH * 128; idx += CT) {
-        const int tt = idx >> 7, i = idx & 127;
-        float a = 0.f, bb = 0.f;
-        if (tt < nt && i < dim) {
+    // (loads in batches of 8: see lightning_chunk_local_kernel)
+    for (int it = 0; it < CH * 128 / CT; it += 8) {
+        float x[8], y[8];
+#pragma unroll
+        for (int u = 0; u < 8; u++) {
+            const int idx = (it + u) * CT + threadIdx.x, tt = idx >> 7, i = idx & 127;
+            const bool ok = tt < nt && i < dim;
             const size_t tok = (size_t)(tok0 + t0 + tt);
-            a = silu_f(to_f32(q[tok * q_stride + (size_t)h * dim + i]));
-            bb = silu_f(to_f32(k[tok * k_stride + (size_t)h * dim + i]));
+            x[u] = ok ? to_f32(q[tok * q_stride + (size_t)h * dim + i]) : 0.f;
+            y[u] = ok ? to_f32(k[tok * k_stride + (size_t)h * dim + i]) : 0.f;
         }
-        qs[tt * LDQ + i] = a;
-        kv[tt * LDQ + i] = bb;
+#pragma unroll
+        for (int u = 0; u < 8; u++) {
+            const int idx = (it + u) * CT + threadIdx.x, tt = idx >> 7, i = idx & 127;
+            const bool ok = tt < nt && i < dim;
+            qs[tt * LDQ + i] = ok ? silu_f(x[u]) : 0.f;
+            kv[tt * LDQ + i] = ok ? silu_f(y[u]) : 0.f;
+        }
     }
     const float* Sg = U + ((size_t)blockIdx.y * n_heads + h) * dim * vdim;
-    for (int idx = threadIdx.x; idx < 128 * VG; idx += CT) {
-        const int i = idx >> 7, j = idx & 127;
-        Ss[idx] = (i < dim && j0 + j < vdim) ? Sg[(size_t)i * vdim + j0 + j] : 0.f;
+    for (int it = 0; it < 128 * VG / CT; it += 8) {
+        float x[8];
+#pragma unroll
+        for (int u = 0; u < 8; u++) {
+            const int idx = (it + u) * CT + threadIdx.x, i = idx >> 7, j = idx & 127;
+            x[u] = (i < dim && j0 + j < vdim) ? Sg[(size_t)i * vdim + j0 + j] : 0.f;
+        }
+#pragma unroll
+        for (int u = 0; u < 8; u++) Ss[(it + u) * CT + threadIdx.x] = x[u];
     }
     for (int i = threadIdx.x; i <= CH; i += CT) pw[i] = powf(lam, (float)i);
     __syncthreads();
@@ -274,11 +292,18 @@ lightning_chunk_out_kernel(const T* __restrict__ q, const T* __restrict__ k, con
             }
     }
     __syncthreads();                     // A is whole, the keys are done with
-    for (int idx = threadIdx.x; idx < CH * VG; idx += CT) {
-        const int tt = idx >> 7, j = idx & 127;
-        float x = 0.f;
-        if (tt < nt && j0 + j < vdim) x = silu_f(to_f32(v[(size_t)(tok0 + t0 + tt) * v_stride + (size_t)h * vdim + j0 + j]));
-        kv[idx] = x;
+    for (int it = 0; it < CH * VG / CT; it += 8) {
+        float x[8];
+#pragma unroll
+        for (int u = 0; u < 8; u++) {
+            const int idx = (it + u) * CT + threadIdx.x, tt = idx >> 7, j = idx & 127;
+            x[u] = (tt < nt && j0 + j < vdim) ? to_f32(v[(size_t)(tok0 + t0 + tt) * v_stride + (size_t)h * vdim + j0 + j]) : 0.f;
+        }
+#pragma unroll
+        for (int u = 0; u < 8; u++) {
+            const int idx = (it + u) * CT + threadIdx.x, tt = idx >> 7, j = idx & 127;
+            kv[idx] = (tt < nt && j0 + j < vdim) ? silu_f(x[u]) : 0.f;
+        }
     }
     float acc[4][8];
 #pragma unroll

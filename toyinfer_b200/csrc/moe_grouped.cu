@@ -171,8 +171,9 @@ moe_grouped_kernel(const T* __restrict__ a, long long lda, const T* __restrict__
 // 128 weight rows, contraction in steps of 64; 8 warps as 2 (places) x 4 (weight rows), a warp 16 x 32.  The tiles of the
 // next step are fetched into registers while this step's are multiplied.  Rows in shared memory are padded by 16 bytes, so
 // that the eight rows a fragment load touches fall into different banks.  Needs K, lda and the matrices' rows in multiples of
-// 8 elements (16-byte loads).
-constexpr int TM = 32, TN = 128, TK = 64, T_THREADS = 256, T_LD = TK + 8;
+// 8 elements (16-byte loads).  With MI = 2 a tile has 64 places (a warp 32 x 32): every weight fragment then feeds two
+// multiplications, which is what the shared memory's bandwidth allows the tensor cores; groups of few places take MI = 1.
+constexpr int TN = 128, TK = 64, T_THREADS = 256, T_LD = TK + 8;
 
 __device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
@@ -180,12 +181,13 @@ __device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4],
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-template <bool PAIR>
+template <bool PAIR, int MI>
 __global__ void __launch_bounds__(T_THREADS)
 moe_grouped_mma_kernel(const bf16* __restrict__ a, long long lda, const bf16* __restrict__ W, const bf16* __restrict__ W2,
                        bf16* __restrict__ out, long long ldo, const int* __restrict__ perm, const int* __restrict__ off,
                        int n_experts, int N, int K, int top, int gather, int scatter, float scale, float limit, float alpha) {
     ti_pdl_trigger();
+    constexpr int TM = 32 * MI;
     __shared__ __align__(16) bf16 As[TM][T_LD];
     __shared__ __align__(16) bf16 Ws[TN][T_LD];
     __shared__ __align__(16) bf16 W2s[PAIR ? TN : 1][T_LD];
@@ -215,15 +217,19 @@ moe_grouped_mma_kernel(const bf16* __restrict__ a, long long lda, const bf16* __
     const bf16* We = W + (size_t)e * N * K;
     const bf16* W2e = PAIR ? W2 + (size_t)e * N * K : nullptr;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int wm = warp >> 2, wn = warp & 3;             // the warp's 16 places and 32 weight rows
+    const int wm = warp >> 2, wn = warp & 3;             // the warp's 16 * MI places and 32 weight rows
     const int g = lane >> 2, t4 = lane & 3;
     // what this thread fetches per step: one 16-byte piece of the places' tile, four of each weight tile
     const int ar = tid >> 3, ac = (tid & 7) * 8;
-    const int a_src = rows[ar];
-    uint4 ra, rw[4], rw2[4];
+    int a_src[MI];
+#pragma unroll
+    for (int i = 0; i < MI; i++) a_src[i] = rows[ar + 32 * i];
+    uint4 ra[MI], rw[4], rw2[4];
     const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
     auto fetch = [&](int k0) {
-        ra = (a_src >= 0 && k0 + ac < K) ? *reinterpret_cast<const uint4*>(a + (size_t)a_src * lda + k0 + ac) : zero;
+#pragma unroll
+        for (int i = 0; i < MI; i++)
+            ra[i] = (a_src[i] >= 0 && k0 + ac < K) ? *reinterpret_cast<const uint4*>(a + (size_t)a_src[i] * lda + k0 + ac) : zero;
 #pragma unroll
         for (int i = 0; i < 4; i++) {
             const int r = (tid >> 3) + 32 * i;
@@ -232,15 +238,18 @@ moe_grouped_mma_kernel(const bf16* __restrict__ a, long long lda, const bf16* __
             if constexpr (PAIR) rw2[i] = ok ? *reinterpret_cast<const uint4*>(W2e + (size_t)(n0 + r) * K + k0 + ac) : zero;
         }
     };
-    float acc[4][4], acc2[PAIR ? 4 : 1][4];
+    float acc[MI][4][4], acc2[MI][PAIR ? 4 : 1][4];
 #pragma unroll
-    for (int i = 0; i < 4; i++)
+    for (int m = 0; m < MI; m++)
 #pragma unroll
-        for (int j = 0; j < 4; j++) { acc[i][j] = 0.f; if constexpr (PAIR) acc2[i][j] = 0.f; }
+        for (int i = 0; i < 4; i++)
+#pragma unroll
+            for (int j = 0; j < 4; j++) { acc[m][i][j] = 0.f; if constexpr (PAIR) acc2[m][i][j] = 0.f; }
     fetch(0);
     for (int k0 = 0; k0 < K; k0 += TK) {
         __syncthreads();             // the last step's reads of the tiles are over
-        *reinterpret_cast<uint4*>(&As[ar][ac]) = ra;
+#pragma unroll
+        for (int i = 0; i < MI; i++) *reinterpret_cast<uint4*>(&As[ar + 32 * i][ac]) = ra[i];
 #pragma unroll
         for (int i = 0; i < 4; i++) {
             *reinterpret_cast<uint4*>(&Ws[(tid >> 3) + 32 * i][ac]) = rw[i];
@@ -250,29 +259,37 @@ moe_grouped_mma_kernel(const bf16* __restrict__ a, long long lda, const bf16* __
         if (k0 + TK < K) fetch(k0 + TK);
 #pragma unroll
         for (int kk = 0; kk < TK; kk += 16) {
-            uint32_t af[4];
-            af[0] = *reinterpret_cast<const uint32_t*>(&As[wm * 16 + g][kk + 2 * t4]);
-            af[1] = *reinterpret_cast<const uint32_t*>(&As[wm * 16 + g + 8][kk + 2 * t4]);
-            af[2] = *reinterpret_cast<const uint32_t*>(&As[wm * 16 + g][kk + 2 * t4 + 8]);
-            af[3] = *reinterpret_cast<const uint32_t*>(&As[wm * 16 + g + 8][kk + 2 * t4 + 8]);
+            uint32_t af[MI][4];
+#pragma unroll
+            for (int m = 0; m < MI; m++) {
+                const int r0 = (wm * MI + m) * 16 + g;
+                af[m][0] = *reinterpret_cast<const uint32_t*>(&As[r0][kk + 2 * t4]);
+                af[m][1] = *reinterpret_cast<const uint32_t*>(&As[r0 + 8][kk + 2 * t4]);
+                af[m][2] = *reinterpret_cast<const uint32_t*>(&As[r0][kk + 2 * t4 + 8]);
+                af[m][3] = *reinterpret_cast<const uint32_t*>(&As[r0 + 8][kk + 2 * t4 + 8]);
+            }
 #pragma unroll
             for (int j = 0; j < 4; j++) {
                 const int n = wn * 32 + j * 8 + g;
                 const uint32_t b0 = *reinterpret_cast<const uint32_t*>(&Ws[n][kk + 2 * t4]);
                 const uint32_t b1 = *reinterpret_cast<const uint32_t*>(&Ws[n][kk + 2 * t4 + 8]);
-                mma_16816(acc[j], af, b0, b1);
+#pragma unroll
+                for (int m = 0; m < MI; m++) mma_16816(acc[m][j], af[m], b0, b1);
                 if constexpr (PAIR) {
                     const uint32_t c0 = *reinterpret_cast<const uint32_t*>(&W2s[n][kk + 2 * t4]);
                     const uint32_t c1 = *reinterpret_cast<const uint32_t*>(&W2s[n][kk + 2 * t4 + 8]);
-                    mma_16816(acc2[j], af, c0, c1);
+#pragma unroll
+                    for (int m = 0; m < MI; m++) mma_16816(acc2[m][j], af[m], c0, c1);
                 }
             }
         }
     }
     // accumulator j: places g (elements 0, 1) and g + 8 (elements 2, 3) of the warp's 16, weight rows j * 8 + 2 t4, + 1
 #pragma unroll
+    for (int m = 0; m < MI; m++)
+#pragma unroll
     for (int half = 0; half < 2; half++) {
-        const int r = wm * 16 + g + 8 * half;
+        const int r = (wm * MI + m) * 16 + g + 8 * half;
         if (r >= cnt) continue;
         const int place = first + r;
         const size_t orow = scatter ? (size_t)perm[place] : (size_t)place;
@@ -284,11 +301,11 @@ moe_grouped_mma_kernel(const bf16* __restrict__ a, long long lda, const bf16* __
                 if (n >= N) continue;
                 float y;
                 if constexpr (PAIR) {
-                    const float gt = fminf(to_f32(from_f32<bf16>(acc[j][2 * half + c])), limit);
-                    const float u = fminf(fmaxf(to_f32(from_f32<bf16>(acc2[j][2 * half + c])), -limit), limit);
+                    const float gt = fminf(to_f32(from_f32<bf16>(acc[m][j][2 * half + c])), limit);
+                    const float u = fminf(fmaxf(to_f32(from_f32<bf16>(acc2[m][j][2 * half + c])), -limit), limit);
                     y = gt * (1.0f / (1.0f + expf(-alpha * gt))) * (u + 1.0f);
                 } else {
-                    y = acc[j][2 * half + c] * scale;
+                    y = acc[m][j][2 * half + c] * scale;
                 }
                 out[orow * ldo + n] = from_f32<bf16>(y);
             }
@@ -345,15 +362,16 @@ extern "C" int ti_moe_grouped(const void* a, long long lda, const void* W, const
     const bool tensor_cores = dtype == TI_BF16 && K % 8 == 0 && lda % 8 == 0 && ((uintptr_t)a & 15) == 0 && ((uintptr_t)W & 15) == 0 &&
                               (!W2 || ((uintptr_t)W2 & 15) == 0);
     if (tensor_cores) {
-        const int tiles = (P + TM - 1) / TM + n_experts;
+        const bool big = P >= 48 * n_experts;         // groups of 48 places and more on average: tiles of 64
+        const int tm = big ? 64 : 32;
+        const int tiles = (P + tm - 1) / tm + n_experts;
         const int nblk = (N + TN - 1) / TN;
         TI_REQUIRE(nblk <= 65535, "moe_grouped: %d weight rows are too many for one launch", N);
-        if (pair)
-            TI_CUDA(ti_launch(moe_grouped_mma_kernel<true>, dim3(tiles, nblk), dim3(T_THREADS), 0, stream, (const bf16*)a, lda,
-                              (const bf16*)W, (const bf16*)W2, (bf16*)out, ldo, perm, off, n_experts, N, K, top, gather, scatter, scale, limit, alpha));
-        else
-            TI_CUDA(ti_launch(moe_grouped_mma_kernel<false>, dim3(tiles, nblk), dim3(T_THREADS), 0, stream, (const bf16*)a, lda,
-                              (const bf16*)W, (const bf16*)W2, (bf16*)out, ldo, perm, off, n_experts, N, K, top, gather, scatter, scale, limit, alpha));
+#define TI_MOE_LAUNCH(PAIR, MI) TI_CUDA(ti_launch(moe_grouped_mma_kernel<PAIR, MI>, dim3(tiles, nblk), dim3(T_THREADS), 0, stream, (const bf16*)a, lda, \
+                              (const bf16*)W, (const bf16*)W2, (bf16*)out, ldo, perm, off, n_experts, N, K, top, gather, scatter, scale, limit, alpha))
+        if (pair) { if (big) TI_MOE_LAUNCH(true, 2); else TI_MOE_LAUNCH(true, 1); }
+        else { if (big) TI_MOE_LAUNCH(false, 2); else TI_MOE_LAUNCH(false, 1); }
+#undef TI_MOE_LAUNCH
         TI_CHECK_LAUNCH("moe_grouped");
         return 0;
     }

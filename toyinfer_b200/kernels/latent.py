@@ -80,11 +80,11 @@ def heads_per_block(n_heads: int, one_token_each: bool) -> int:
 
 
 def decode_splits(n_seq: int, n_heads: int, hb: int, span: int, sms: int) -> int:
-    """Blocks that share a sequence's keys when every sequence brings one query: about two blocks per SM in all, a tile
-    of 32 keys each at least, 64 at most."""
+    """Blocks that share a sequence's keys when every sequence brings one query: about one block per SM in all (every
+    split costs the merging kernel a row of partial sums), a tile of 32 keys each at least, 64 at most."""
     tiles = span // 32 + 2
     groups = (n_heads + hb - 1) // hb
-    return max(1, min((2 * sms) // max(1, n_seq * groups), tiles, 64))
+    return max(1, min(sms // max(1, n_seq * groups), tiles, 64))
 
 
 def plan(n_seq: int, n_heads: int, window: int, plan_len: int, device) -> int:
