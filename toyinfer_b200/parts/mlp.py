@@ -1,4 +1,7 @@
-"""Dense gated feed-forward (SwiGLU).
+"""Feed-forwards: dense gated (SwiGLU), dense squared-ReLU, and table-routed mixture of experts (the latter two at the
+end of the file).
+
+SwiGLU:
 
 gate = Wg x, up = Wu x, z = up * gate / (1 + exp(-gate)) with the activation and the
 product in 32-bit and one rounding, y = Wd z; no bias.  Reference:
