@@ -259,7 +259,7 @@ def test_squared_relu_feed_forward(dtype):
 
 
 @pytest.mark.parametrize("dtype", DT)
-@pytest.mark.parametrize("experts,top,M", [(5, 2, 70), (3, 1, 1), (4, 4, 9), (40, 3, 200), (2, 2, 130)])
+@pytest.mark.parametrize("experts,top,M", [(5, 2, 70), (3, 1, 1), (4, 4, 9), (40, 3, 200), (2, 2, 130), (3, 1, 400)])
 @pytest.mark.parametrize("hidden,ff", [(40, 36), (136, 200)])
 def test_table_routed_experts(dtype, experts, top, M, hidden, ff):
     """(Rows of 40 and 36 elements run on the CUDA cores in both types; 136 and 200 on the tensor cores in bfloat16.)"""

@@ -73,7 +73,8 @@ template <typename T, bool PAIR>
 __global__ void __launch_bounds__(G_THREADS)
 moe_grouped_kernel(const T* __restrict__ a, long long lda, const T* __restrict__ W, const T* __restrict__ W2,
                    T* __restrict__ out, long long ldo, const int* __restrict__ perm, const int* __restrict__ off,
-                   int n_experts, int N, int K, int top, int gather, int scatter, float scale, float limit, float alpha) {
+                   int n_experts, int N, int K, int top, int gather, int scatter, float scale, float limit, float alpha,
+                   long long w_estride) {
     ti_pdl_trigger();
     __shared__ float As[GK][GM + 1];
     __shared__ float Ws[GK][GN + 1];
@@ -104,8 +105,8 @@ moe_grouped_kernel(const T* __restrict__ a, long long lda, const T* __restrict__
         rows[threadIdx.x] = r;
     }
     __syncthreads();
-    const T* We = W + (size_t)e * N * K;
-    const T* W2e = PAIR ? W2 + (size_t)e * N * K : nullptr;
+    const T* We = W + (size_t)e * w_estride;
+    const T* W2e = PAIR ? W2 + (size_t)e * w_estride : nullptr;
     // thread (ty, tx): places ty, ty + 8, ty + 16, ty + 24; weight rows tx, tx + 32
     const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
     float acc[4][2], acc2[4][2];
@@ -185,7 +186,8 @@ template <bool PAIR, int MI>
 __global__ void __launch_bounds__(T_THREADS)
 moe_grouped_mma_kernel(const bf16* __restrict__ a, long long lda, const bf16* __restrict__ W, const bf16* __restrict__ W2,
                        bf16* __restrict__ out, long long ldo, const int* __restrict__ perm, const int* __restrict__ off,
-                       int n_experts, int N, int K, int top, int gather, int scatter, float scale, float limit, float alpha) {
+                       int n_experts, int N, int K, int top, int gather, int scatter, float scale, float limit, float alpha,
+                       long long w_estride) {
     ti_pdl_trigger();
     constexpr int TM = 32 * MI;
     __shared__ __align__(16) bf16 As[TM][T_LD];
@@ -214,8 +216,8 @@ moe_grouped_mma_kernel(const bf16* __restrict__ a, long long lda, const bf16* __
         rows[threadIdx.x] = threadIdx.x < cnt ? (gather ? perm[i] / top : i) : -1;
     }
     __syncthreads();
-    const bf16* We = W + (size_t)e * N * K;
-    const bf16* W2e = PAIR ? W2 + (size_t)e * N * K : nullptr;
+    const bf16* We = W + (size_t)e * w_estride;
+    const bf16* W2e = PAIR ? W2 + (size_t)e * w_estride : nullptr;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int wm = warp >> 2, wn = warp & 3;             // the warp's 16 * MI places and 32 weight rows
     const int g = lane >> 2, t4 = lane & 3;
@@ -325,6 +327,87 @@ __global__ void moe_combine_kernel(const T* __restrict__ z, T* __restrict__ out,
     }
 }
 
+// For the tcgen05 grouped product: every expert's places padded to whole tiles of 128.  pad_src[i] is the token row that
+// padded place i takes its input from (-1: a padding row), pad_of_pair[p] the padded place of pair p, tile_group[t] the
+// expert of tile t (-1: none).  One block.
+__global__ void moe_pad_plan_kernel(const int* __restrict__ perm, const int* __restrict__ off, int n_experts, int P, int top,
+                                    int rows, int* __restrict__ pad_src, int* __restrict__ pad_of_pair, int* __restrict__ tile_group) {
+    ti_pdl_trigger();
+    extern __shared__ int poff[];        // [n_experts + 1] padded offsets
+    ti_pdl_sync();
+    perm = ti_dependent(perm); off = ti_dependent(off);
+    if (threadIdx.x == 0) {
+        int a = 0;
+        for (int e = 0; e < n_experts; e++) { poff[e] = a; a += (off[e + 1] - off[e] + 127) / 128 * 128; }
+        poff[n_experts] = a;
+    }
+    for (int i = threadIdx.x; i < rows; i += blockDim.x) pad_src[i] = -1;
+    __syncthreads();
+    for (int t = threadIdx.x; t < rows / 128; t += blockDim.x) {
+        int g = -1;
+        for (int e = 0; e < n_experts; e++)
+            if (t * 128 >= poff[e] && t * 128 < poff[e + 1]) { g = e; break; }
+        tile_group[t] = g;
+    }
+    for (int e = 0; e < n_experts; e++) {
+        const int lo = off[e], cnt = off[e + 1] - lo;
+        for (int i = threadIdx.x; i < cnt; i += blockDim.x) {
+            const int p = perm[lo + i], at = poff[e] + i;
+            pad_src[at] = p / top;
+            pad_of_pair[p] = at;
+        }
+    }
+}
+
+template <typename T>
+__global__ void moe_gather_rows_kernel(const T* __restrict__ x, long long ldx, const int* __restrict__ pad_src, T* __restrict__ xs, int H) {
+    ti_pdl_trigger();
+    ti_pdl_sync();
+    x = ti_dependent(x); pad_src = ti_dependent(pad_src);
+    const size_t i = blockIdx.x;
+    const int src = pad_src[i];
+    if ((H & 7) == 0 && sizeof(T) == 2) {
+        const uint4* s4 = src >= 0 ? reinterpret_cast<const uint4*>(x + (size_t)src * ldx) : nullptr;
+        uint4* d4 = reinterpret_cast<uint4*>(xs + i * H);
+        for (int e = threadIdx.x; e < H / 8; e += blockDim.x) d4[e] = s4 ? s4[e] : make_uint4(0u, 0u, 0u, 0u);
+    } else {
+        for (int e = threadIdx.x; e < H; e += blockDim.x) xs[i * H + e] = src >= 0 ? x[(size_t)src * ldx + e] : from_f32<T>(0.f);
+    }
+}
+
+// gu[i] = [gate (ff) | up (ff)] -> y[i] = g' sigmoid(alpha g') (u' + 1)
+template <typename T>
+__global__ void moe_act_pair_kernel(const T* __restrict__ gu, T* __restrict__ y, int ff, long long total, float limit, float alpha) {
+    ti_pdl_trigger();
+    ti_pdl_sync();
+    gu = ti_dependent(gu);
+    for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total; idx += (long long)gridDim.x * blockDim.x) {
+        const long long i = idx / ff;
+        const int f = (int)(idx - i * ff);
+        const float g = fminf(to_f32(gu[i * 2 * ff + f]), limit);
+        const float u = fminf(fmaxf(to_f32(gu[i * 2 * ff + ff + f]), -limit), limit);
+        y[idx] = from_f32<T>(g * (1.0f / (1.0f + expf(-alpha * g))) * (u + 1.0f));
+    }
+}
+
+// out[m] = sum_j z[pad_of_pair[m * top + j]] * weight, each term rounded as the scattering product would have stored it
+template <typename T>
+__global__ void moe_combine_indexed_kernel(const T* __restrict__ z, const int* __restrict__ pad_of_pair, T* __restrict__ out, int H,
+                                           int top, float weight) {
+    ti_pdl_trigger();
+    ti_pdl_sync();
+    z = ti_dependent(z); pad_of_pair = ti_dependent(pad_of_pair);
+    const size_t m = blockIdx.x;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float s = 0.f;
+        for (int j = 0; j < top; j++) {
+            const float term = to_f32(from_f32<T>(to_f32(z[(size_t)pad_of_pair[m * top + j] * H + i]) * weight));
+            s = j == 0 ? term : s + term;
+        }
+        out[m * H + i] = from_f32<T>(s);
+    }
+}
+
 template <typename T>
 __global__ void relu2_kernel(const T* __restrict__ x, T* __restrict__ out, long long n) {
     ti_pdl_trigger();
@@ -355,8 +438,10 @@ extern "C" int ti_moe_route_table(const int* ids, const int* table, int vocab, i
 // P places.  pair != 0: out[i, 0:N] = act(a_i W[e]^T, a_i W2[e]^T).  Else out[(scatter ? perm[i] : i)] = a_i W[e]^T * scale.
 extern "C" int ti_moe_grouped(const void* a, long long lda, const void* W, const void* W2, void* out, long long ldo,
                               const int* perm, const int* off, int n_experts, int P, int N, int K, int top, int gather,
-                              int scatter, int pair, float scale, float limit, float alpha, int dtype, cudaStream_t stream) {
+                              int scatter, int pair, float scale, float limit, float alpha, long long w_estride, int dtype,
+                              cudaStream_t stream) {
     if (P == 0) return 0;
+    if (w_estride <= 0) w_estride = (long long)N * K;          // elements from one expert's matrix to the next
     TI_REQUIRE(P > 0 && N > 0 && K > 0 && n_experts > 0 && top > 0, "moe_grouped: bad sizes");
     TI_REQUIRE(!pair || W2, "moe_grouped: the paired form needs a second matrix");
     const bool tensor_cores = dtype == TI_BF16 && K % 8 == 0 && lda % 8 == 0 && ((uintptr_t)a & 15) == 0 && ((uintptr_t)W & 15) == 0 &&
@@ -368,7 +453,7 @@ extern "C" int ti_moe_grouped(const void* a, long long lda, const void* W, const
         const int nblk = (N + TN - 1) / TN;
         TI_REQUIRE(nblk <= 65535, "moe_grouped: %d weight rows are too many for one launch", N);
 #define TI_MOE_LAUNCH(PAIR, MI) TI_CUDA(ti_launch(moe_grouped_mma_kernel<PAIR, MI>, dim3(tiles, nblk), dim3(T_THREADS), 0, stream, (const bf16*)a, lda, \
-                              (const bf16*)W, (const bf16*)W2, (bf16*)out, ldo, perm, off, n_experts, N, K, top, gather, scatter, scale, limit, alpha))
+                              (const bf16*)W, (const bf16*)W2, (bf16*)out, ldo, perm, off, n_experts, N, K, top, gather, scatter, scale, limit, alpha, w_estride))
         if (pair) { if (big) TI_MOE_LAUNCH(true, 2); else TI_MOE_LAUNCH(true, 1); }
         else { if (big) TI_MOE_LAUNCH(false, 2); else TI_MOE_LAUNCH(false, 1); }
 #undef TI_MOE_LAUNCH
@@ -382,10 +467,10 @@ extern "C" int ti_moe_grouped(const void* a, long long lda, const void* W, const
         using T = decltype(t);
         if (pair)
             TI_CUDA(ti_launch(moe_grouped_kernel<T, true>, dim3(tiles, nblk), dim3(G_THREADS), 0, stream, (const T*)a, lda,
-                              (const T*)W, (const T*)W2, (T*)out, ldo, perm, off, n_experts, N, K, top, gather, scatter, scale, limit, alpha));
+                              (const T*)W, (const T*)W2, (T*)out, ldo, perm, off, n_experts, N, K, top, gather, scatter, scale, limit, alpha, w_estride));
         else
             TI_CUDA(ti_launch(moe_grouped_kernel<T, false>, dim3(tiles, nblk), dim3(G_THREADS), 0, stream, (const T*)a, lda,
-                              (const T*)W, (const T*)W2, (T*)out, ldo, perm, off, n_experts, N, K, top, gather, scatter, scale, limit, alpha));
+                              (const T*)W, (const T*)W2, (T*)out, ldo, perm, off, n_experts, N, K, top, gather, scatter, scale, limit, alpha, w_estride));
         TI_CHECK_LAUNCH("moe_grouped");
         return 0;
     });
@@ -398,6 +483,59 @@ extern "C" int ti_moe_combine(const void* z, void* out, int M, int H, int top, i
         using T = decltype(t);
         TI_CUDA(ti_launch_class<1>(moe_combine_kernel<T>, dim3(M), dim3(H <= 256 ? 64 : 256), 0, stream, (const T*)z, (T*)out, H, top));
         TI_CHECK_LAUNCH("moe_combine");
+        return 0;
+    });
+}
+
+extern "C" int ti_moe_pad_plan(const int* perm, const int* off, int n_experts, int P, int top, int rows, int* pad_src,
+                               int* pad_of_pair, int* tile_group, cudaStream_t stream) {
+    if (P == 0) return 0;
+    TI_REQUIRE(P > 0 && n_experts > 0 && top > 0 && rows % 128 == 0 && rows >= P + 0, "moe_pad_plan: bad sizes");
+    const size_t smem = (size_t)(n_experts + 1) * sizeof(int);
+    TI_REQUIRE(smem <= 48 * 1024, "moe_pad_plan: %d experts are too many", n_experts);
+    TI_CUDA(ti_launch_class<1>(moe_pad_plan_kernel, dim3(1), dim3(1024), smem, stream, perm, off, n_experts, P, top, rows, pad_src,
+                               pad_of_pair, tile_group));
+    TI_CHECK_LAUNCH("moe_pad_plan");
+    return 0;
+}
+
+extern "C" int ti_moe_gather_rows(const void* x, long long ldx, const int* pad_src, void* xs, int rows, int H, int dtype,
+                                  cudaStream_t stream) {
+    if (rows == 0) return 0;
+    TI_REQUIRE(rows > 0 && H > 0, "moe_gather_rows: bad sizes");
+    return ti_dispatch_dtype(dtype, [&](auto t) -> int {
+        using T = decltype(t);
+        TI_REQUIRE(sizeof(T) != 2 || (H & 7) || ((((uintptr_t)x | (uintptr_t)xs) & 15) == 0 && ldx % 8 == 0),
+                   "moe_gather_rows: rows are not 16-byte aligned");
+        TI_CUDA(ti_launch_class<1>(moe_gather_rows_kernel<T>, dim3(rows), dim3(128), 0, stream, (const T*)x, ldx, pad_src, (T*)xs, H));
+        TI_CHECK_LAUNCH("moe_gather_rows");
+        return 0;
+    });
+}
+
+extern "C" int ti_moe_act_pair(const void* gu, void* y, long long rows, int ff, float limit, float alpha, int dtype, cudaStream_t stream) {
+    if (rows == 0) return 0;
+    TI_REQUIRE(rows > 0 && ff > 0, "moe_act_pair: bad sizes");
+    return ti_dispatch_dtype(dtype, [&](auto t) -> int {
+        using T = decltype(t);
+        const long long n = rows * ff;
+        const long long want = (n + 255) / 256;
+        TI_CUDA(ti_launch_class<1>(moe_act_pair_kernel<T>, dim3((unsigned)(want < 148 * 16 ? want : 148 * 16)), dim3(256), 0, stream,
+                                   (const T*)gu, (T*)y, ff, n, limit, alpha));
+        TI_CHECK_LAUNCH("moe_act_pair");
+        return 0;
+    });
+}
+
+extern "C" int ti_moe_combine_indexed(const void* z, const int* pad_of_pair, void* out, int M, int H, int top, float weight, int dtype,
+                                      cudaStream_t stream) {
+    if (M == 0) return 0;
+    TI_REQUIRE(M > 0 && H > 0 && top > 0, "moe_combine_indexed: bad sizes");
+    return ti_dispatch_dtype(dtype, [&](auto t) -> int {
+        using T = decltype(t);
+        TI_CUDA(ti_launch_class<1>(moe_combine_indexed_kernel<T>, dim3(M), dim3(H <= 256 ? 64 : 256), 0, stream, (const T*)z, pad_of_pair,
+                                   (T*)out, H, top, weight));
+        TI_CHECK_LAUNCH("moe_combine_indexed");
         return 0;
     });
 }

@@ -38,27 +38,57 @@ def route_by_table(ids: torch.Tensor, table: torch.Tensor, n_experts: int):
     return perm, off
 
 
-def experts_ffn(x: torch.Tensor, perm: torch.Tensor, off: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor,
-                w_down: torch.Tensor, top: int, limit: float, alpha: float, weight: float) -> torch.Tensor:
-    """x[M, H]; w_gate, w_up [experts, ff, H]; w_down [experts, H, ff].  Every pair's expert output times ``weight``,
-    summed per token in the order of its choices -> [M, H]."""
-    _need_cuda(x, perm, off, w_gate, w_up, w_down, what="moe")
+TC_MIN_GROUP = 64          # places per expert on average from which the tcgen05 grouped product runs (groups are padded to 128)
+
+
+def experts_ffn(x: torch.Tensor, perm: torch.Tensor, off: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, top: int,
+                limit: float, alpha: float, weight: float) -> torch.Tensor:
+    """x[M, H]; w_gate_up [experts, 2 * ff, H] (an expert's gate rows, then its up rows); w_down [experts, H, ff].  Every
+    pair's expert output times ``weight``, summed per token in the order of its choices -> [M, H].
+
+    bfloat16 steps with many tokens per expert pad every expert's tokens to tiles of 128 rows and run both products on
+    tcgen05 (csrc/gemm_tcgen05_grouped.cu); everything else runs the grouped tiles of csrc/moe_grouped.cu."""
+    _need_cuda(x, perm, off, w_gate_up, w_down, what="moe")
     M, H = x.shape
-    E, ff, H2 = w_gate.shape
-    if H2 != H or w_up.shape != w_gate.shape or w_down.shape != (E, H, ff) or x.stride(1) != 1:
+    E, ff2, H2 = w_gate_up.shape
+    ff = ff2 // 2
+    if H2 != H or ff2 != 2 * ff or w_down.shape != (E, H, ff) or x.stride(1) != 1:
         raise KernelError("moe: the experts' matrices do not fit the tokens")
-    for t in (w_gate, w_up, w_down):
+    for t in (w_gate_up, w_down):
         if t.dtype != x.dtype or not t.is_contiguous():
             raise KernelError("moe: the experts' matrices must be dense and of the tokens' dtype")
     Pn = M * top
     code = _code(x, "moe")
-    fn = _fn("ti_moe_grouped", [P, L, P, P, P, L, P, P, I, I, I, I, I, I, I, I, F, F, F, I, P])
+    if (x.dtype == torch.bfloat16 and H % 8 == 0 and ff % 8 == 0 and Pn >= TC_MIN_GROUP * E and x.stride(0) % 8 == 0
+            and x.data_ptr() % 16 == 0):
+        rows = (Pn + 127 * E + 127) // 128 * 128
+        dev = x.device
+        pad_src = torch.empty(rows, dtype=torch.int32, device=dev)
+        pad_of_pair = torch.empty(Pn, dtype=torch.int32, device=dev)
+        tile_group = torch.empty(rows // 128, dtype=torch.int32, device=dev)
+        _call(_fn("ti_moe_pad_plan", [P, P, I, I, I, I, P, P, P, P]), _ptr(perm), _ptr(off), E, Pn, top, rows, _ptr(pad_src),
+              _ptr(pad_of_pair), _ptr(tile_group), _stream())
+        xs = torch.empty((rows, H), dtype=x.dtype, device=dev)
+        _call(_fn("ti_moe_gather_rows", [P, L, P, P, I, I, I, P]), _ptr(x), x.stride(0), _ptr(pad_src), _ptr(xs), rows, H, code, _stream())
+        grouped = _fn("ti_linear_grouped_tc", [P, P, P, P, I, I, I, I, L, P])
+        gu = torch.empty((rows, 2 * ff), dtype=x.dtype, device=dev)
+        _call(grouped, _ptr(xs), _ptr(w_gate_up), _ptr(gu), _ptr(tile_group), rows, E, 2 * ff, H, 2 * ff, _stream())
+        y = torch.empty((rows, ff), dtype=x.dtype, device=dev)
+        _call(_fn("ti_moe_act_pair", [P, P, L, I, F, F, I, P]), _ptr(gu), _ptr(y), rows, ff, float(limit), float(alpha), code, _stream())
+        z = torch.empty((rows, H), dtype=x.dtype, device=dev)
+        _call(grouped, _ptr(y), _ptr(w_down), _ptr(z), _ptr(tile_group), rows, E, H, ff, H, _stream())
+        out = torch.empty((M, H), dtype=x.dtype, device=dev)
+        _call(_fn("ti_moe_combine_indexed", [P, P, P, I, I, I, F, I, P]), _ptr(z), _ptr(pad_of_pair), _ptr(out), M, H, top, float(weight),
+              code, _stream())
+        return out
+    fn = _fn("ti_moe_grouped", [P, L, P, P, P, L, P, P, I, I, I, I, I, I, I, I, F, F, F, L, I, P])
     y = torch.empty((Pn, ff), dtype=x.dtype, device=x.device)
-    _call(fn, _ptr(x), x.stride(0), _ptr(w_gate), _ptr(w_up), _ptr(y), ff, _ptr(perm), _ptr(off), E, Pn, ff, H, top, 1, 0, 1,
-          1.0, float(limit), float(alpha), code, _stream())
+    w_up = w_gate_up[:, ff:]          # the same storage, an expert's up rows after its gate rows
+    _call(fn, _ptr(x), x.stride(0), _ptr(w_gate_up), _ptr(w_up), _ptr(y), ff, _ptr(perm), _ptr(off), E, Pn, ff, H, top, 1, 0, 1,
+          1.0, float(limit), float(alpha), 2 * ff * H, code, _stream())
     z = torch.empty((Pn, H), dtype=x.dtype, device=x.device)
     _call(fn, _ptr(y), ff, _ptr(w_down), None, _ptr(z), H, _ptr(perm), _ptr(off), E, Pn, H, ff, top, 0, 1, 0,
-          float(weight), 0.0, 0.0, code, _stream())
+          float(weight), 0.0, 0.0, 0, code, _stream())
     if top == 1:
         return z
     out = torch.empty((M, H), dtype=x.dtype, device=x.device)

@@ -99,7 +99,7 @@ class TableMoE(FeedForward):
         n = {"expert": "e{}.", "gate": "gate", "up": "up", "down": "down", "table": "table"}
         n.update(names or {})
         self.prefix, self.n = prefix, n
-        self.w_gate = self.w_up = self.w_down = self.table = None
+        self.w_gate_up = self.w_down = self.table = None
 
     def _name(self, e: int, which: str) -> str:
         return self.prefix + self.n["expert"].format(e) + self.n[which]
@@ -116,8 +116,9 @@ class TableMoE(FeedForward):
 
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
         E = range(self.n_experts)
-        self.w_gate = torch.stack([tensors.pop(self._name(e, "gate")) for e in E]).contiguous()
-        self.w_up = torch.stack([tensors.pop(self._name(e, "up")) for e in E]).contiguous()
+        # an expert's gate rows, then its up rows: one product makes both
+        self.w_gate_up = torch.stack([torch.cat([tensors.pop(self._name(e, "gate")), tensors.pop(self._name(e, "up"))], dim=0)
+                                      for e in E]).contiguous()
         self.w_down = torch.stack([tensors.pop(self._name(e, "down")) for e in E]).contiguous()
         self.table = tensors.pop(self.prefix + self.n["table"]).to(torch.int32).contiguous()
 
@@ -127,8 +128,7 @@ class TableMoE(FeedForward):
             raise RuntimeError("a table-routed feed-forward needs the step's token ids")
         ids = batch.token_ids[: x.shape[0]]
         perm, off = KM.route_by_table(ids, self.table, self.n_experts)
-        return KM.experts_ffn(x, perm, off, self.w_gate, self.w_up, self.w_down, self.top, self.limit, self.alpha,
-                              1.0 / self.top)
+        return KM.experts_ffn(x, perm, off, self.w_gate_up, self.w_down, self.top, self.limit, self.alpha, 1.0 / self.top)
 
 
 register_part("feed_forward", "relu2", SquaredReLU)
