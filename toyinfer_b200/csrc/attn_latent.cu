@@ -54,19 +54,15 @@ __device__ __forceinline__ void store_row_to_pages(const LatentPages& kv, int sl
 
 // ---------------------------------------------------------------------------
 template <typename T>
-__global__ void latent_prep_kernel(const T* __restrict__ d, long long d_stride, T* __restrict__ q, long long q_stride,
-                                   int n_heads, int plain, int rank, int rot, const float* __restrict__ norm_w, float eps,
-                                   const float* __restrict__ cos_t, const float* __restrict__ sin_t, int max_pos,
-                                   const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
-                                   const int* __restrict__ seq_slot, T* __restrict__ lat, LatentPages kv) {
-    ti_pdl_trigger();
-    extern __shared__ float sm[];        // W floats, then W values of T, then 33
+__device__ __forceinline__ void latent_prep_body(float* sm, const T* d, long long d_stride, T* q, long long q_stride,
+                                                 int n_heads, int plain, int rank, int rot, const float* __restrict__ norm_w, float eps,
+                                                 const float* __restrict__ cos_t, const float* __restrict__ sin_t, int max_pos,
+                                                 const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
+                                                 const int* __restrict__ seq_slot, T* __restrict__ lat, const LatentPages& kv) {
     const int W = rank + rot;
-    float* vals = sm;
+    float* vals = sm;                    // W floats, then 33, then W values of T
     float* red = sm + W;
     T* rounded = reinterpret_cast<T*>(red + 33);
-    ti_pdl_sync();
-    d = ti_dependent(d); q = ti_dependent(q);
     const int m = blockIdx.x, t = threadIdx.x, nt = blockDim.x;
     const int pos = min(max(tok_pos[m], 0), max_pos - 1);
     const int half = rot >> 1;
@@ -100,6 +96,127 @@ __global__ void latent_prep_kernel(const T* __restrict__ d, long long d_stride, 
             const float u = to_f32(p[i]), v = to_f32(p[i + half]), c = cs[i], s = sn[i];
             p[i] = from_f32<T>(u * c - v * s);
             p[i + half] = from_f32<T>(v * c + u * s);
+        }
+    }
+}
+
+template <typename T>
+__global__ void latent_prep_kernel(const T* __restrict__ d, long long d_stride, T* __restrict__ q, long long q_stride,
+                                   int n_heads, int plain, int rank, int rot, const float* __restrict__ norm_w, float eps,
+                                   const float* __restrict__ cos_t, const float* __restrict__ sin_t, int max_pos,
+                                   const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
+                                   const int* __restrict__ seq_slot, T* __restrict__ lat, LatentPages kv) {
+    ti_pdl_trigger();
+    extern __shared__ float sm[];
+    ti_pdl_sync();
+    d = ti_dependent(d); q = ti_dependent(q);
+    latent_prep_body<T>(sm, d, d_stride, q, q_stride, n_heads, plain, rank, rot, norm_w, eps, cos_t, sin_t, max_pos, tok_pos, tok_seq,
+                        seq_slot, lat, kv);
+}
+
+// For steps of few tokens: the work of latent_prep and latent_absorb in one launch.  Grid (tokens, heads + 1): block
+// (m, h) with h < heads carries head h of token m into the latent space (the rotated part is rotated on the way, q itself
+// stays as it is); block (m, heads) does the token's row.
+template <typename T>
+__global__ void __launch_bounds__(128)
+latent_prep_absorb_kernel(const T* __restrict__ d, long long d_stride, const T* __restrict__ q, long long q_stride,
+                          int n_heads, int plain, int rank, int rot, const float* __restrict__ norm_w, float eps,
+                          const float* __restrict__ cos_t, const float* __restrict__ sin_t, int max_pos,
+                          const int* __restrict__ tok_pos, const int* __restrict__ tok_seq, const int* __restrict__ seq_slot,
+                          T* __restrict__ lat, LatentPages kv, const T* __restrict__ uk, float* __restrict__ qa) {
+    ti_pdl_trigger();
+    extern __shared__ float sm[];
+    ti_pdl_sync();
+    d = ti_dependent(d); q = ti_dependent(q);
+    if ((int)blockIdx.y == n_heads) {
+        latent_prep_body<T>(sm, d, d_stride, (T*)nullptr, 0, n_heads, plain, rank, rot, norm_w, eps, cos_t, sin_t, max_pos, tok_pos,
+                            tok_seq, seq_slot, lat, kv);
+        return;
+    }
+    const int m = blockIdx.x, h = blockIdx.y, t = threadIdx.x;
+    const int hd = plain + rot, W = rank + rot, half = rot >> 1;
+    const T* qh = q + (size_t)m * q_stride + (size_t)h * hd;
+    float* qs = sm;                      // [plain]
+    for (int i = t; i < plain; i += 128) qs[i] = to_f32(qh[i]);
+    float* dst = qa + ((size_t)m * n_heads + h) * W;
+    if (rot) {
+        const int pos = min(max(tok_pos[m], 0), max_pos - 1);
+        for (int i = t; i < half; i += 128) {
+            // (rounded to the engine's type as the rotation in place would have left it)
+            const float u = to_f32(qh[plain + i]), v = to_f32(qh[plain + i + half]);
+            const float c = cos_t[(size_t)pos * half + i], sn = sin_t[(size_t)pos * half + i];
+            dst[rank + i] = to_f32(from_f32<T>(u * c - v * sn));
+            dst[rank + i + half] = to_f32(from_f32<T>(v * c + u * sn));
+        }
+    }
+    __syncthreads();
+    const T* ukh = uk + (size_t)h * plain * rank;
+    for (int r0 = 0; r0 < rank; r0 += 128 * 4) {
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 4
+        for (int dd = 0; dd < plain; dd++) {
+            const float qv = qs[dd];
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const int r = r0 + t + 128 * j;
+                if (r < rank) acc[j] = fmaf(qv, to_f32(ukh[(size_t)dd * rank + r]), acc[j]);
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const int r = r0 + t + 128 * j;
+            if (r < rank) dst[r] = acc[j];
+        }
+    }
+}
+
+// For steps of few tokens: the merge of the key splits and the way out through Wuv in one launch.  Block (token, head):
+// the splits' unnormalised sums are weighed and added into the latent result (shared memory), then
+// o[v] = sum_r uv[h, v, r] * result[r], a warp per output element, four elements at a time.
+template <typename T>
+__global__ void __launch_bounds__(128)
+latent_merge_expand_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, const T* __restrict__ uv,
+                           T* __restrict__ o, long long o_stride, int n_heads, int vdim, int rank, int n_splits) {
+    ti_pdl_trigger();
+    extern __shared__ float res[];       // [rank], then [64] weights
+    float* w_s = res + rank;
+    ti_pdl_sync();
+    part_o = ti_dependent(part_o); part_ml = ti_dependent(part_ml);
+    const int b = blockIdx.x, h = blockIdx.y, t = threadIdx.x;
+    const size_t base = ((size_t)b * n_heads + h) * n_splits;
+    float m = -INFINITY;
+    for (int s = 0; s < n_splits; s++) m = fmaxf(m, part_ml[(base + s) * 2]);
+    float l = 0.f;
+    for (int s = 0; s < n_splits; s++) {
+        const float ms = part_ml[(base + s) * 2];
+        const float w = ms > -INFINITY ? expf(ms - m) : 0.f;
+        if (t == 0) w_s[s] = w;
+        l += w > 0.f ? w * part_ml[(base + s) * 2 + 1] : 0.f;
+    }
+    __syncthreads();
+    const float inv = l > 0.f ? 1.f / l : 0.f;
+    for (int e = t; e < rank; e += 128) {
+        float acc = 0.f;
+        for (int s = 0; s < n_splits; s++) {
+            const float w = w_s[s];
+            if (w > 0.f) acc = fmaf(w, part_o[(base + s) * rank + e], acc);      // an empty split's numbers were never written
+        }
+        res[e] = acc * inv;
+    }
+    __syncthreads();
+    const int warp = t >> 5, lane = t & 31;
+    for (int v0 = warp * 4; v0 < vdim; v0 += 16) {
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int r = lane; r < rank; r += 32) {
+            const float x = res[r];
+#pragma unroll
+            for (int j = 0; j < 4; j++)
+                if (v0 + j < vdim) acc[j] = fmaf(to_f32(uv[((size_t)h * vdim + v0 + j) * rank + r]), x, acc[j]);
+        }
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const float sum = warp_sum(acc[j]);
+            if (lane == 0 && v0 + j < vdim) o[(size_t)b * o_stride + (size_t)h * vdim + v0 + j] = from_f32<T>(sum);
         }
     }
 }
@@ -564,7 +681,7 @@ latent_decode_mma_kernel(const float* __restrict__ qa, const bf16* __restrict__ 
             const int r = mt * 16 + g + 8 * half, h = h0 + r;
             if (h >= n_heads) continue;
             const float l = l_s[r];
-            if (n_splits > 1) {
+            if (part_o != nullptr) {
                 const size_t at = ((size_t)tok * n_heads + h) * n_splits + split;
                 if (t4 == 0 && warp == 0) { part_ml[at * 2] = m_s[r]; part_ml[at * 2 + 1] = l; }
 #pragma unroll
@@ -590,7 +707,8 @@ latent_decode_mma_kernel(const float* __restrict__ qa, const bf16* __restrict__ 
 template <int MT, int NTW>
 int launch_decode_mma(const float* qa, const void* lat, float* ol, const int* cu_new, const int* seq_start, const int* seq_slot,
                       int n_seq, int n_heads, int rank, int rot, float scale, int window, const float* sink,
-                      const LatentPages& kv, int n_splits, float* part_o, float* part_ml, int n_tok, cudaStream_t stream) {
+                      const LatentPages& kv, int n_splits, float* part_o, float* part_ml, int n_tok, cudaStream_t stream,
+                      const void* uv = nullptr, void* o = nullptr, long long o_stride = 0, int vdim = 0) {
     constexpr int ROWS = 16 * MT;
     const int W = rank + rot, LD = W + 8;
     const size_t smem = (size_t)(ROWS + DK) * LD * 2 + (size_t)ROWS * (DK + 8) * 2 + ((size_t)ROWS * (DK + 1) + 3 * ROWS) * 4;
@@ -603,6 +721,13 @@ int launch_decode_mma(const float* qa, const void* lat, float* ol, const int* cu
     TI_CUDA(ti_launch_class<3>(latent_decode_mma_kernel<MT, NTW>, grid, dim3(D_THREADS), smem, stream, qa, (const bf16*)lat, ol, cu_new,
                                seq_start, seq_slot, n_heads, rank, rot, scale, window, sink, kv, n_splits, part_o, part_ml));
     TI_CHECK_LAUNCH("latent_attention (one token, tensor cores)");
+    if (uv) {
+        const size_t sm2 = (size_t)(rank + 64) * sizeof(float);
+        TI_CUDA(ti_launch_class<4>(latent_merge_expand_kernel<bf16>, dim3(n_tok, n_heads), dim3(128), sm2, stream, (const float*)part_o,
+                                   (const float*)part_ml, (const bf16*)uv, (bf16*)o, o_stride, n_heads, vdim, rank, n_splits));
+        TI_CHECK_LAUNCH("latent_merge_expand");
+        return 0;
+    }
     if (n_splits > 1) {
         int threads = ((rank + 3) / 4 + 31) / 32 * 32;
         TI_CUDA(ti_launch_class<4>(tiattn::attn_decode_combine_kernel<float>, dim3(n_tok, n_heads), dim3(threads), 0, stream,
@@ -681,6 +806,61 @@ extern "C" int ti_latent_store(const void* lat, int W, const int* tok_pos, const
         TI_CHECK_LAUNCH("latent_store");
         return 0;
     });
+}
+
+// A step of single tokens in two launches before and two after the projections... the latent's part of it: this one does
+// latent_prep's and latent_absorb's work (q is left unrotated; qa gets the rotated part).
+extern "C" int ti_latent_prep_absorb(const void* d, long long d_stride, const void* q, long long q_stride, int n_heads, int plain,
+                                     int rank, int rot, const float* norm_w, float eps, const float* cos_t, const float* sin_t,
+                                     int max_pos, const int* tok_pos, const int* tok_seq, const int* seq_slot, const int* seq_len,
+                                     void* lat, void* pages, const int* page_table, int table_width, int page_size, int ring_rows,
+                                     int n_pages, const void* uk, float* qa, int M, int dtype, cudaStream_t stream) {
+    if (M == 0) return 0;
+    TI_REQUIRE(M > 0 && n_heads > 0 && n_heads < 65535 && rank > 0 && rot >= 0 && rot % 2 == 0 && plain >= 0 && q && uk && qa && lat,
+               "latent_prep_absorb: bad arguments");
+    TI_REQUIRE(rot == 0 || (cos_t && sin_t && max_pos > 0), "latent_prep_absorb: a rotated part needs cos and sin tables");
+    TI_REQUIRE(!pages || (page_table && seq_len && page_size > 0 && table_width > 0 && n_pages > 0 && ring_rows % page_size == 0),
+               "latent_prep_absorb: incomplete cache description");
+    LatentPages kv{pages, page_table, table_width, page_size, ring_rows, n_pages, seq_len};
+    const int W = rank + rot;
+    return ti_dispatch_dtype(dtype, [&](auto t) -> int {
+        using T = decltype(t);
+        size_t smem = (size_t)(W + 33) * sizeof(float) + (size_t)W * sizeof(T);
+        if ((size_t)plain * sizeof(float) > smem) smem = (size_t)plain * sizeof(float);
+        TI_REQUIRE(smem <= 48 * 1024, "latent_prep_absorb: rows of %d elements are too long", W);
+        TI_CUDA(ti_launch_class<2>(latent_prep_absorb_kernel<T>, dim3(M, n_heads + 1), dim3(128), smem, stream, (const T*)d, d_stride,
+                                   (const T*)q, q_stride, n_heads, plain, rank, rot, norm_w, eps, cos_t, sin_t, max_pos, tok_pos, tok_seq,
+                                   seq_slot, (T*)lat, kv, (const T*)uk, qa));
+        TI_CHECK_LAUNCH("latent_prep_absorb");
+        return 0;
+    });
+}
+
+// Whether ti_latent_decode takes these sizes (bfloat16 only): rows in 16-element steps, a latent in 8-element tiles up to 512.
+extern "C" int ti_latent_decode_takes(int rank, int rot) { return (rank + rot) % 16 == 0 && rank % 8 == 0 && rank <= 512; }
+
+// One query per sequence, bfloat16, tensor cores; the key splits' merge and the way out through uv[heads * vdim, rank] in
+// the second launch: o[n_seq, heads * vdim].  part_o: float32 [n_seq, heads, n_splits, rank], part_ml: [n_seq, heads, n_splits, 2].
+extern "C" int ti_latent_decode(const float* qa, const void* lat, const int* cu_new, const int* seq_start, const int* seq_slot,
+                                int n_seq, int n_heads, int rank, int rot, float scale, int window, const float* sink,
+                                const void* pages, const int* page_table, int table_width, int page_size, int ring_rows, int n_pages,
+                                int n_splits, float* part_o, float* part_ml, const void* uv, void* o, long long o_stride, int vdim,
+                                cudaStream_t stream) {
+    if (n_seq == 0) return 0;
+    TI_REQUIRE(n_seq > 0 && n_seq <= 65535 && n_heads > 0 && vdim > 0 && ti_latent_decode_takes(rank, rot), "latent_decode: sizes not taken");
+    TI_REQUIRE(n_splits >= 1 && n_splits <= 64 && part_o && part_ml && uv && o, "latent_decode: bad arguments");
+    TI_REQUIRE(pages && page_table && page_size > 0 && table_width > 0 && n_pages > 0 && ring_rows % page_size == 0,
+               "latent_decode: incomplete cache description");
+    TI_REQUIRE(ring_rows == 0 || (window > 0 && ring_rows >= window), "latent_decode: a ring of %d rows needs a window of at most as many", ring_rows);
+    TI_REQUIRE((((uintptr_t)lat | (uintptr_t)pages | (uintptr_t)qa) & 15) == 0, "latent_decode: rows are not 16-byte aligned");
+    LatentPages kv{const_cast<void*>(pages), page_table, table_width, page_size, ring_rows, n_pages, nullptr};
+    const bool two = n_heads > 16;
+#define TI_LATENT_DECODE(MT, NTW) launch_decode_mma<MT, NTW>(qa, lat, nullptr, cu_new, seq_start, seq_slot, n_seq, n_heads, rank, rot, scale, \
+                                                            window, sink, kv, n_splits, part_o, part_ml, n_seq, stream, uv, o, o_stride, vdim)
+    if (rank <= 128) return two ? TI_LATENT_DECODE(2, 4) : TI_LATENT_DECODE(1, 4);
+    if (rank <= 256) return two ? TI_LATENT_DECODE(2, 8) : TI_LATENT_DECODE(1, 8);
+    return two ? TI_LATENT_DECODE(2, 16) : TI_LATENT_DECODE(1, 16);
+#undef TI_LATENT_DECODE
 }
 
 extern "C" int ti_latent_pack(const void* q, long long q_stride, const void* ku, const void* lat, void* Qp, void* Kp, void* Vp,

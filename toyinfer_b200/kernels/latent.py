@@ -131,6 +131,47 @@ def prompt_eligible(q: torch.Tensor, lat: torch.Tensor, rank: int, rot: int, vdi
     return prompt_heads(q.shape[2] - rot, rot, vdim)
 
 
+def single_eligible(q: torch.Tensor, rank: int, rot: int, batch, mem) -> bool:
+    """Whether attention_single takes this step: every sequence one token, bfloat16, sizes the tensor-core kernel takes."""
+    return (batch.mode == "extend" and q.dtype == torch.bfloat16 and (rank + rot) % 16 == 0 and rank % 8 == 0 and rank <= 512
+            and mem.k_pages.dtype == torch.bfloat16 and mem.k_pages.data_ptr() % 16 == 0)
+
+
+def attention_single(d: torch.Tensor, q: torch.Tensor, rank: int, rot: int, norm_w: torch.Tensor, eps: float, tables,
+                     uk: torch.Tensor, uv: torch.Tensor, vdim: int, scale: float, window: int, sink: Optional[torch.Tensor],
+                     batch, mem) -> torch.Tensor:
+    """A step in which every sequence brings one token, bfloat16, in three launches: the token's row (normed, rotated, stored)
+    together with its queries' way into the latent space; the attention over the cached rows on the tensor cores, a
+    sequence's keys split over blocks; the splits' merge together with the way out through uv.  d[M, rank + rot] and
+    q[M, heads, plain + rot] are the projection's output as it is -> [M, heads * vdim]."""
+    _need_cuda(d, q, norm_w, uk, uv, sink, what="latent_attention")
+    M, nh, hd = q.shape
+    plain, W = hd - rot, rank + rot
+    _check_mem(mem, W, q.dtype, "latent_attention")
+    cos = sin = None
+    max_pos = 0
+    if rot:
+        cos, sin, dim = tables
+        max_pos = cos.shape[0]
+        if dim != rot or batch.max_pos_after > max_pos:
+            raise KernelError(f"latent_attention: position {batch.max_pos_after - 1} is beyond the rotary tables' {max_pos}")
+    lat = torch.empty((M, W), dtype=q.dtype, device=q.device)
+    qa = torch.empty((M, nh, W), dtype=torch.float32, device=q.device)
+    _call(_fn("ti_latent_prep_absorb", [P, L, P, L, I, I, I, I, P, F, P, P, I, P, P, P, P, P, P, P, I, I, I, I, P, P, I, I, P]),
+          _ptr(d), d.stride(0), _ptr(q), q.stride(0), nh, plain, rank, rot, _ptr(norm_w), float(eps), _ptr(cos), _ptr(sin), max_pos,
+          _ptr(batch.tok_pos), _ptr(batch.tok_seq), _ptr(batch.seq_slot), _ptr(batch.seq_len), _ptr(lat), *_pages(mem), _ptr(uk),
+          _ptr(qa), M, _code(q, "latent_attention"), _stream())
+    splits = plan(batch.n_seq, nh, window, batch.plan_len, q.device)
+    part_o = torch.empty((M, nh, splits, rank), dtype=torch.float32, device=q.device)
+    part_ml = torch.empty((M, nh, splits, 2), dtype=torch.float32, device=q.device)
+    o = torch.empty((M, nh * vdim), dtype=q.dtype, device=q.device)
+    _call(_fn("ti_latent_decode", [P, P, P, P, P, I, I, I, I, F, I, P, P, P, I, I, I, I, I, P, P, P, P, L, I, P]),
+          _ptr(qa), _ptr(lat), _ptr(batch.cu_new), _ptr(batch.seq_start), _ptr(batch.seq_slot), batch.n_seq, nh, rank, rot,
+          float(scale), int(window), _ptr(sink), *_pages(mem), splits, _ptr(part_o), _ptr(part_ml), _ptr(uv), _ptr(o), o.stride(0),
+          vdim, _stream(), launches=2)
+    return o
+
+
 def attention(q: torch.Tensor, lat: torch.Tensor, uk: torch.Tensor, uv: torch.Tensor, vdim: int, rank: int, rot: int,
               scale: float, window: int, sink: Optional[torch.Tensor], batch, mem) -> torch.Tensor:
     """q[M, heads, plain + rot] (rotated part already rotated), the step's rows lat[M, rank + rot], uk[heads * plain, rank],

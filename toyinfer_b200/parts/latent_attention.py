@@ -110,20 +110,26 @@ class LatentAttention(Mixer):
         q = qd[:, : H * hd].view(M, H, hd)
         d = qd[:, H * hd:]
         with ranged(batch, "mixer.attention"):
-            # In a ring, a long run of new rows overwrites positions that the run's first queries still read:
-            # such a step stores after its attention (which takes the step's own rows from the step anyway).
-            store_first = not (batch.mode == "mixed" and mem.ring_rows > 0)
             tables = self.pos.rotary_tables() if self.pos is not None else None
-            lat = KL.prep(d, q, self.rank, self.rot, self.norm_w, self.eps, tables, batch, mem if store_first else None)
-            D = KL.prompt_eligible(q, lat, self.rank, self.rot, self.vdim, batch) if self.w_ukv is not None else 0
-            if D:
-                a = KL.attention_prompt(q, lat, self.w_ukv, self.vdim, self.rank, self.rot, self.scale, self.window,
-                                        self.sink, batch, D)
+            D = 0
+            if KL.single_eligible(q, self.rank, self.rot, batch, mem):
+                # one token each: three launches from the projection's output to the output projection's input
+                a = KL.attention_single(d, q, self.rank, self.rot, self.norm_w, self.eps, tables, self.w_uk, self.w_uv, self.vdim,
+                                        self.scale, self.window, self.sink, batch, mem)
             else:
-                a = KL.attention(q, lat, self.w_uk, self.w_uv, self.vdim, self.rank, self.rot, self.scale, self.window,
-                                 self.sink, batch, mem)
-            if not store_first:
-                KL.store(lat, batch, mem)
+                # In a ring, a long run of new rows overwrites positions that the run's first queries still read:
+                # such a step stores after its attention (which takes the step's own rows from the step anyway).
+                store_first = not (batch.mode == "mixed" and mem.ring_rows > 0)
+                lat = KL.prep(d, q, self.rank, self.rot, self.norm_w, self.eps, tables, batch, mem if store_first else None)
+                D = KL.prompt_eligible(q, lat, self.rank, self.rot, self.vdim, batch) if self.w_ukv is not None else 0
+                if D:
+                    a = KL.attention_prompt(q, lat, self.w_ukv, self.vdim, self.rank, self.rot, self.scale, self.window,
+                                            self.sink, batch, D)
+                else:
+                    a = KL.attention(q, lat, self.w_uk, self.w_uv, self.vdim, self.rank, self.rot, self.scale, self.window,
+                                     self.sink, batch, mem)
+                if not store_first:
+                    KL.store(lat, batch, mem)
         with ranged(batch, "mixer.out"):
             return K.linear(a, self.w_o_padded if D else self.w_o)
 
