@@ -153,7 +153,7 @@ latent_prep_absorb_kernel(const T* __restrict__ d, long long d_stride, const T* 
     const T* ukh = uk + (size_t)h * plain * rank;
     for (int r0 = 0; r0 < rank; r0 += 128 * 4) {
         float acc[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll 4
+#pragma unroll 8
         for (int dd = 0; dd < plain; dd++) {
             const float qv = qs[dd];
 #pragma unroll
@@ -205,6 +205,30 @@ latent_merge_expand_kernel(const float* __restrict__ part_o, const float* __rest
     }
     __syncthreads();
     const int warp = t >> 5, lane = t & 31;
+    if (sizeof(T) == 2 && (rank & 7) == 0 && (reinterpret_cast<uintptr_t>(uv) & 15) == 0) {
+        // 16-byte pieces of four rows at a time: eight loads on their way per lane
+        for (int v0 = warp * 4; v0 < vdim; v0 += 16) {
+            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+            for (int c = lane; c < (rank >> 3); c += 32) {
+                uint4 w[4];
+#pragma unroll
+                for (int j = 0; j < 4; j++)
+                    w[j] = v0 + j < vdim ? reinterpret_cast<const uint4*>(uv + ((size_t)h * vdim + v0 + j) * rank)[c] : make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const bf16* wv = reinterpret_cast<const bf16*>(&w[j]);
+#pragma unroll
+                    for (int e = 0; e < 8; e++) acc[j] = fmaf(to_f32(wv[e]), res[c * 8 + e], acc[j]);
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const float sum = warp_sum(acc[j]);
+                if (lane == 0 && v0 + j < vdim) o[(size_t)b * o_stride + (size_t)h * vdim + v0 + j] = from_f32<T>(sum);
+            }
+        }
+        return;
+    }
     for (int v0 = warp * 4; v0 < vdim; v0 += 16) {
         float acc[4] = {0.f, 0.f, 0.f, 0.f};
         for (int r = lane; r < rank; r += 32) {

@@ -375,6 +375,48 @@ __global__ void moe_gather_rows_kernel(const T* __restrict__ x, long long ldx, c
     }
 }
 
+// the same over 16-byte pieces of bfloat16 (ff a multiple of 8)
+__global__ void moe_act_pair_vec_kernel(const bf16* __restrict__ gu, bf16* __restrict__ y, int ff8, long long total, float limit, float alpha) {
+    ti_pdl_trigger();
+    ti_pdl_sync();
+    gu = ti_dependent(gu);
+    for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total; idx += (long long)gridDim.x * blockDim.x) {
+        const long long i = idx / ff8;
+        const int c = (int)(idx - i * ff8);
+        const uint4 g4 = reinterpret_cast<const uint4*>(gu)[i * 2 * ff8 + c], u4 = reinterpret_cast<const uint4*>(gu)[i * 2 * ff8 + ff8 + c];
+        const bf16* gp = reinterpret_cast<const bf16*>(&g4);
+        const bf16* up = reinterpret_cast<const bf16*>(&u4);
+        uint4 o4;
+        bf16* op = reinterpret_cast<bf16*>(&o4);
+#pragma unroll
+        for (int e = 0; e < 8; e++) {
+            const float g = fminf(to_f32(gp[e]), limit);
+            const float u = fminf(fmaxf(to_f32(up[e]), -limit), limit);
+            op[e] = from_f32<bf16>(g * (1.0f / (1.0f + expf(-alpha * g))) * (u + 1.0f));
+        }
+        reinterpret_cast<uint4*>(y)[idx] = o4;
+    }
+}
+
+// the squared ReLU over 16-byte pieces of bfloat16
+__global__ void relu2_vec_kernel(const bf16* __restrict__ x, bf16* __restrict__ out, long long n8) {
+    ti_pdl_trigger();
+    ti_pdl_sync();
+    x = ti_dependent(x);
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n8; i += (long long)gridDim.x * blockDim.x) {
+        const uint4 v4 = reinterpret_cast<const uint4*>(x)[i];
+        const bf16* vp = reinterpret_cast<const bf16*>(&v4);
+        uint4 o4;
+        bf16* op = reinterpret_cast<bf16*>(&o4);
+#pragma unroll
+        for (int e = 0; e < 8; e++) {
+            const float v = fmaxf(to_f32(vp[e]), 0.f);
+            op[e] = from_f32<bf16>(v * v);
+        }
+        reinterpret_cast<uint4*>(out)[i] = o4;
+    }
+}
+
 // gu[i] = [gate (ff) | up (ff)] -> y[i] = g' sigmoid(alpha g') (u' + 1)
 template <typename T>
 __global__ void moe_act_pair_kernel(const T* __restrict__ gu, T* __restrict__ y, int ff, long long total, float limit, float alpha) {
@@ -516,6 +558,14 @@ extern "C" int ti_moe_gather_rows(const void* x, long long ldx, const int* pad_s
 extern "C" int ti_moe_act_pair(const void* gu, void* y, long long rows, int ff, float limit, float alpha, int dtype, cudaStream_t stream) {
     if (rows == 0) return 0;
     TI_REQUIRE(rows > 0 && ff > 0, "moe_act_pair: bad sizes");
+    if (dtype == TI_BF16 && ff % 8 == 0 && (((uintptr_t)gu | (uintptr_t)y) & 15) == 0) {
+        const long long n = rows * (ff / 8);
+        const long long want = (n + 255) / 256;
+        TI_CUDA(ti_launch_class<1>(moe_act_pair_vec_kernel, dim3((unsigned)(want < 148 * 16 ? want : 148 * 16)), dim3(256), 0, stream,
+                                   (const bf16*)gu, (bf16*)y, ff / 8, n, limit, alpha));
+        TI_CHECK_LAUNCH("moe_act_pair");
+        return 0;
+    }
     return ti_dispatch_dtype(dtype, [&](auto t) -> int {
         using T = decltype(t);
         const long long n = rows * ff;
@@ -543,6 +593,13 @@ extern "C" int ti_moe_combine_indexed(const void* z, const int* pad_of_pair, voi
 extern "C" int ti_relu2(const void* x, void* out, long long n, int dtype, cudaStream_t stream) {
     if (n == 0) return 0;
     TI_REQUIRE(n > 0, "relu2: bad size");
+    if (dtype == TI_BF16 && n % 8 == 0 && (((uintptr_t)x | (uintptr_t)out) & 15) == 0) {
+        const long long n8 = n / 8, want = (n8 + 255) / 256;
+        TI_CUDA(ti_launch_class<1>(relu2_vec_kernel, dim3((unsigned)(want < 148 * 16 ? want : 148 * 16)), dim3(256), 0, stream,
+                                   (const bf16*)x, (bf16*)out, n8));
+        TI_CHECK_LAUNCH("relu2");
+        return 0;
+    }
     return ti_dispatch_dtype(dtype, [&](auto t) -> int {
         using T = decltype(t);
         const int threads = 256;
