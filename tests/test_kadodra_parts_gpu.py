@@ -94,6 +94,11 @@ LATENT = [
     dict(heads=2, dim=64, rot=64, vdim=128, rank=64, window=100, scaling=None),
     dict(heads=3, dim=32, rot=32, vdim=64, rank=32, window=0, scaling=None),
     dict(heads=2, dim=40, rot=32, vdim=72, rank=16, window=65, scaling={"factor": 2.0, "original": 40, "fast": 4.0, "slow": 1.0}),
+    # more heads than one tensor-core tile of 16 rows holds, and more than two; latents of more than 128 and 256 elements
+    dict(heads=20, dim=8, rot=8, vdim=8, rank=24, window=50, scaling=None),
+    dict(heads=40, dim=8, rot=8, vdim=16, rank=40, window=0, scaling=None),
+    dict(heads=3, dim=8, rot=24, vdim=8, rank=136, window=0, scaling=None),
+    dict(heads=2, dim=8, rot=8, vdim=8, rank=264, window=70, scaling=None),
 ]
 
 
