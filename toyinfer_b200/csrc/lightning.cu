@@ -126,6 +126,7 @@ lightning_chunk_local_kernel(const T* __restrict__ k, const T* __restrict__ v, l
     extern __shared__ float sm[];
     float* ks = sm;                      // [CH][128]  (lam^(nt-1-s) k_s, zero past dim)
     float* vs = ks + CH * 128;           // [CH][VG]
+    __shared__ float pw[CH];             // lam^(nt-1-s)
     ti_pdl_sync();
     k = ti_dependent(k); v = ti_dependent(v);
     const int h = blockIdx.x / groups, g = blockIdx.x - h * groups;
@@ -133,6 +134,8 @@ lightning_chunk_local_kernel(const T* __restrict__ k, const T* __restrict__ v, l
     if (!find_chunk(cz, blockIdx.y, b, c, tok0, n)) return;
     const int t0 = c * CH, nt = min(CH, n - t0), j0 = g * VG;
     const float lam = decay[h];
+    if (threadIdx.x < CH) pw[threadIdx.x] = threadIdx.x < nt ? powf(lam, (float)(nt - 1 - (int)threadIdx.x)) : 0.f;
+    __syncthreads();
     // (loads in batches of 8, so that eight are on their way at a time: a block's few warps cannot hide one load each)
     for (int it = 0; it < CH * 128 / CT; it += 8) {
         float x[8], y[8];
@@ -145,7 +148,7 @@ lightning_chunk_local_kernel(const T* __restrict__ k, const T* __restrict__ v, l
 #pragma unroll
         for (int u = 0; u < 8; u++) {
             const int idx = (it + u) * CT + threadIdx.x, tt = idx >> 7, i = idx & 127;
-            ks[idx] = (tt < nt && i < dim) ? silu_f(x[u]) * powf(lam, (float)(nt - 1 - tt)) : 0.f;
+            ks[idx] = (tt < nt && i < dim) ? silu_f(x[u]) * pw[tt] : 0.f;
             vs[idx] = (tt < nt && j0 + i < vdim) ? silu_f(y[u]) : 0.f;
         }
     }
@@ -200,22 +203,31 @@ __global__ void lightning_chunk_scan_kernel(float* __restrict__ U, float* __rest
     float* u = U + ((size_t)first * n_heads + h) * dim * vdim + e;
     const size_t step = (size_t)n_heads * dim * vdim;
     float S = *sp;
-    float own = *u;
-    for (int c = 0; c < nchunks; c++) {
-        const float next = c + 1 < nchunks ? u[step] : 0.f;      // asked for before this chunk's store
-        *u = S;
-        S = fmaf(c + 1 < nchunks ? whole : rest, S, own);
-        own = next;
-        u += step;
+    // a chunk's own contribution is read before the state before it is stored in its place; eight reads go out together
+    for (int c0 = 0; c0 < nchunks; c0 += 8) {
+        float own[8];
+#pragma unroll
+        for (int j = 0; j < 8; j++) own[j] = c0 + j < nchunks ? u[(size_t)j * step] : 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            if (c0 + j < nchunks) {
+                u[(size_t)j * step] = S;
+                S = fmaf(c0 + j + 1 < nchunks ? whole : rest, S, own[j]);
+            }
+        }
+        u += 8 * step;
     }
     *sp = S;
 }
 
 // (3) outputs of a chunk, O = diag(lam^(t+1)) Q S + A V with A[t][s] = lam^(t-s) (q_t . k_s) for s <= t, S the state before
 // the chunk: A is formed first (a [nt x dim] x [dim x nt] product), then the two products add into the same registers.
-// Thread (ty, tx) of 16 x 16: tokens t = ty + 16 a (a < 4), columns j = 8 tx .. 8 tx + 7.
+// 512 threads (the operands leave room for one block per SM: sixteen warps hide more than eight): thread (ty, tx) of
+// 16 x 32 has tokens t = ty + 16 a (a < 4) and columns j = 4 tx .. 4 tx + 3.
+constexpr int CO = 512;
+
 template <typename T>
-__global__ void __launch_bounds__(CT)
+__global__ void __launch_bounds__(CO)
 lightning_chunk_out_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v,
                            long long q_stride, long long k_stride, long long v_stride,
                            const float* __restrict__ U, float* __restrict__ o,
@@ -235,12 +247,13 @@ lightning_chunk_out_kernel(const T* __restrict__ q, const T* __restrict__ k, con
     if (!find_chunk(cz, blockIdx.y, b, c, tok0, n)) return;
     const int t0 = c * CH, nt = min(CH, n - t0), j0 = g * VG;
     const float lam = decay[h];
+    const int tid = threadIdx.x;
     // (loads in batches of 8: see lightning_chunk_local_kernel)
-    for (int it = 0; it < CH * 128 / CT; it += 8) {
+    for (int it = 0; it < CH * 128 / CO; it += 8) {
         float x[8], y[8];
 #pragma unroll
         for (int u = 0; u < 8; u++) {
-            const int idx = (it + u) * CT + threadIdx.x, tt = idx >> 7, i = idx & 127;
+            const int idx = (it + u) * CO + tid, tt = idx >> 7, i = idx & 127;
             const bool ok = tt < nt && i < dim;
             const size_t tok = (size_t)(tok0 + t0 + tt);
             x[u] = ok ? to_f32(q[tok * q_stride + (size_t)h * dim + i]) : 0.f;
@@ -248,94 +261,91 @@ lightning_chunk_out_kernel(const T* __restrict__ q, const T* __restrict__ k, con
         }
 #pragma unroll
         for (int u = 0; u < 8; u++) {
-            const int idx = (it + u) * CT + threadIdx.x, tt = idx >> 7, i = idx & 127;
+            const int idx = (it + u) * CO + tid, tt = idx >> 7, i = idx & 127;
             const bool ok = tt < nt && i < dim;
             qs[tt * LDQ + i] = ok ? silu_f(x[u]) : 0.f;
             kv[tt * LDQ + i] = ok ? silu_f(y[u]) : 0.f;
         }
     }
     const float* Sg = U + ((size_t)blockIdx.y * n_heads + h) * dim * vdim;
-    for (int it = 0; it < 128 * VG / CT; it += 8) {
+    for (int it = 0; it < 128 * VG / CO; it += 8) {
         float x[8];
 #pragma unroll
         for (int u = 0; u < 8; u++) {
-            const int idx = (it + u) * CT + threadIdx.x, i = idx >> 7, j = idx & 127;
+            const int idx = (it + u) * CO + tid, i = idx >> 7, j = idx & 127;
             x[u] = (i < dim && j0 + j < vdim) ? Sg[(size_t)i * vdim + j0 + j] : 0.f;
         }
 #pragma unroll
-        for (int u = 0; u < 8; u++) Ss[(it + u) * CT + threadIdx.x] = x[u];
+        for (int u = 0; u < 8; u++) Ss[(it + u) * CO + tid] = x[u];
     }
-    for (int i = threadIdx.x; i <= CH; i += CT) pw[i] = powf(lam, (float)i);
+    for (int i = tid; i <= CH; i += CO) pw[i] = powf(lam, (float)i);
     __syncthreads();
-    const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;
-    {   // A: tokens t = ty + 16 a, keys s = tx + 16 e (a, e < 4)
-        float acc[4][4];
+    const int ty = tid >> 5, tx = tid & 31;
+    {   // A: tokens t = ty + 16 a (a < 4), keys s = tx + 32 e (e < 2)
+        float acc[4][2];
 #pragma unroll
-        for (int a = 0; a < 4; a++)
-#pragma unroll
-            for (int e = 0; e < 4; e++) acc[a][e] = 0.f;
+        for (int a = 0; a < 4; a++) { acc[a][0] = 0.f; acc[a][1] = 0.f; }
         for (int i = 0; i < dim; i++) {
-            float qv[4], kk[4];
+            float qv[4];
 #pragma unroll
-            for (int a = 0; a < 4; a++) { qv[a] = qs[(ty + 16 * a) * LDQ + i]; kk[a] = kv[(tx + 16 * a) * LDQ + i]; }
+            for (int a = 0; a < 4; a++) qv[a] = qs[(ty + 16 * a) * LDQ + i];
+            const float k0 = kv[tx * LDQ + i], k1 = kv[(tx + 32) * LDQ + i];
 #pragma unroll
-            for (int a = 0; a < 4; a++)
-#pragma unroll
-                for (int e = 0; e < 4; e++) acc[a][e] = fmaf(qv[a], kk[e], acc[a][e]);
+            for (int a = 0; a < 4; a++) { acc[a][0] = fmaf(qv[a], k0, acc[a][0]); acc[a][1] = fmaf(qv[a], k1, acc[a][1]); }
         }
 #pragma unroll
         for (int a = 0; a < 4; a++)
 #pragma unroll
-            for (int e = 0; e < 4; e++) {
-                const int tt = ty + 16 * a, ss = tx + 16 * e;
+            for (int e = 0; e < 2; e++) {
+                const int tt = ty + 16 * a, ss = tx + 32 * e;
                 A[tt * (CH + 1) + ss] = (ss <= tt && tt < nt) ? acc[a][e] * pw[tt - ss] : 0.f;
             }
     }
     __syncthreads();                     // A is whole, the keys are done with
-    for (int it = 0; it < CH * VG / CT; it += 8) {
+    for (int it = 0; it < CH * VG / CO; it += 8) {
         float x[8];
 #pragma unroll
         for (int u = 0; u < 8; u++) {
-            const int idx = (it + u) * CT + threadIdx.x, tt = idx >> 7, j = idx & 127;
+            const int idx = (it + u) * CO + tid, tt = idx >> 7, j = idx & 127;
             x[u] = (tt < nt && j0 + j < vdim) ? to_f32(v[(size_t)(tok0 + t0 + tt) * v_stride + (size_t)h * vdim + j0 + j]) : 0.f;
         }
 #pragma unroll
         for (int u = 0; u < 8; u++) {
-            const int idx = (it + u) * CT + threadIdx.x, tt = idx >> 7, j = idx & 127;
+            const int idx = (it + u) * CO + tid, tt = idx >> 7, j = idx & 127;
             kv[idx] = (tt < nt && j0 + j < vdim) ? silu_f(x[u]) : 0.f;
         }
     }
-    float acc[4][8];
+    float acc[4][4];
 #pragma unroll
     for (int a = 0; a < 4; a++)
 #pragma unroll
-        for (int e = 0; e < 8; e++) acc[a][e] = 0.f;
+        for (int e = 0; e < 4; e++) acc[a][e] = 0.f;
     for (int i = 0; i < dim; i++) {
-        float qv[4], sv[8];
+        float qv[4];
 #pragma unroll
         for (int a = 0; a < 4; a++) qv[a] = qs[(ty + 16 * a) * LDQ + i];
-        const float4 s0 = *reinterpret_cast<const float4*>(Ss + i * VG + 8 * tx), s1 = *reinterpret_cast<const float4*>(Ss + i * VG + 8 * tx + 4);
-        sv[0] = s0.x; sv[1] = s0.y; sv[2] = s0.z; sv[3] = s0.w; sv[4] = s1.x; sv[5] = s1.y; sv[6] = s1.z; sv[7] = s1.w;
+        const float4 s0 = *reinterpret_cast<const float4*>(Ss + i * VG + 4 * tx);
+        const float sv[4] = {s0.x, s0.y, s0.z, s0.w};
 #pragma unroll
         for (int a = 0; a < 4; a++)
 #pragma unroll
-            for (int e = 0; e < 8; e++) acc[a][e] = fmaf(qv[a], sv[e], acc[a][e]);
+            for (int e = 0; e < 4; e++) acc[a][e] = fmaf(qv[a], sv[e], acc[a][e]);
     }
 #pragma unroll
     for (int a = 0; a < 4; a++)
 #pragma unroll
-        for (int e = 0; e < 8; e++) acc[a][e] *= pw[ty + 16 * a + 1];
+        for (int e = 0; e < 4; e++) acc[a][e] *= pw[ty + 16 * a + 1];
     __syncthreads();                     // the values are in place
     for (int ss = 0; ss < nt; ss++) {
-        float av[4], vv[8];
+        float av[4];
 #pragma unroll
         for (int a = 0; a < 4; a++) av[a] = A[(ty + 16 * a) * (CH + 1) + ss];
-        const float4 v0 = *reinterpret_cast<const float4*>(kv + ss * VG + 8 * tx), v1 = *reinterpret_cast<const float4*>(kv + ss * VG + 8 * tx + 4);
-        vv[0] = v0.x; vv[1] = v0.y; vv[2] = v0.z; vv[3] = v0.w; vv[4] = v1.x; vv[5] = v1.y; vv[6] = v1.z; vv[7] = v1.w;
+        const float4 v0 = *reinterpret_cast<const float4*>(kv + ss * VG + 4 * tx);
+        const float vv[4] = {v0.x, v0.y, v0.z, v0.w};
 #pragma unroll
         for (int a = 0; a < 4; a++)
 #pragma unroll
-            for (int e = 0; e < 8; e++) acc[a][e] = fmaf(av[a], vv[e], acc[a][e]);
+            for (int e = 0; e < 4; e++) acc[a][e] = fmaf(av[a], vv[e], acc[a][e]);
     }
 #pragma unroll
     for (int a = 0; a < 4; a++) {
@@ -343,8 +353,8 @@ lightning_chunk_out_kernel(const T* __restrict__ q, const T* __restrict__ k, con
         if (tt >= nt) continue;
         float* orow = o + (size_t)(tok0 + t0 + tt) * ((size_t)n_heads * vdim) + (size_t)h * vdim;
 #pragma unroll
-        for (int e = 0; e < 8; e++) {
-            const int j = j0 + 8 * tx + e;
+        for (int e = 0; e < 4; e++) {
+            const int j = j0 + 4 * tx + e;
             if (j < vdim) orow[j] = acc[a][e];
         }
     }
@@ -433,7 +443,7 @@ extern "C" int ti_lightning_chunked(const void* q, const void* k, const void* v,
         TI_CUDA(ti_launch(lightning_chunk_scan_kernel, dim3((dim * vdim + 127) / 128, n_heads, n_seq), dim3(128), 0, stream,
                           U, state, decay, cz, n_heads, dim, vdim));
         TI_CHECK_LAUNCH("lightning_chunk_scan");
-        TI_CUDA(ti_launch(lightning_chunk_out_kernel<T>, dim3(n_heads * groups, n_chunks), dim3(CT), smem3, stream,
+        TI_CUDA(ti_launch(lightning_chunk_out_kernel<T>, dim3(n_heads * groups, n_chunks), dim3(CO), smem3, stream,
                           (const T*)q, (const T*)k, (const T*)v, q_stride, k_stride, v_stride, (const float*)U, o, decay, cz,
                           n_heads, dim, vdim, groups));
         TI_CHECK_LAUNCH("lightning_chunk_out");
