@@ -151,3 +151,47 @@ def test_trace_runner_on_a_folder(folders, tmp_path, dtype):
     for k in range(10):
         rows = [wa[90 + k]] + ([wb[30 + k]] if (k < 7 and k % 2) else [])
         assert_close_logits(read(k + 1), torch.stack(rows), dtype, f"step {k + 1}")
+
+
+@pytest.mark.parametrize("name", ["P", "R"])
+def test_prompt_shapes_that_come_back_run_from_a_captured_step(folders, name):
+    """The same shape of prompt step four times, in other slots each time and with other tokens: from the third time on the
+    engine replays a captured graph (states zeroed at hand-out, slots and tokens read on the device), and every run gives what
+    the plain implementation gives."""
+    eng = engine(folders[name], "float32")
+    assert eng.prompt_graph_tokens > 0
+    held = []
+    for rep in range(4):
+        ids = prompts(name, [40, 17], seed=20 + rep)
+        slots = [eng.new_sequence() for _ in ids]
+        got = eng.step(list(zip(slots, ids))).clone()
+        for i, x in enumerate(ids):
+            assert_close_logits(got[i:i + 1], plain_logits(folders[name], x)[-1:], "float32", f"{name} run {rep} prompt {i}")
+        # one decode step after it, so that what the prompt step left (cache rows, states) is read
+        nxt = [3 + rep, 5]
+        got = eng.step([(s, [t]) for s, t in zip(slots, nxt)]).clone()
+        for i, x in enumerate(ids):
+            assert_close_logits(got[i:i + 1], plain_logits(folders[name], list(x) + [nxt[i]])[-1:], "float32", f"{name} run {rep} next {i}")
+        if rep % 2:
+            for s in slots:
+                eng.end_sequence(s)
+        else:
+            held.extend(slots)          # these stay live: the next run gets other slots
+    assert eng.graph_replays >= 2
+
+
+def test_command_line_generates_from_a_folder(folders):
+    cmd = [sys.executable, os.path.join(ROOT, "bin", "toyinfer"), "--model_dir", folders["Q"], "--dtype", "float32", "--max_seq_len", "128",
+           "--prompt_ids", "5,6,7;8,9", "--max_new_tokens", "6", "--temperature", "0"]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stderr[-2000:]
+    first = json.loads(r.stdout.strip().splitlines()[0])
+    assert first["request"] == 0 and len(first["tokens"]) == 6
+    w, cfg = read_folder(folders["Q"])
+    seq = [5, 6, 7]
+    for t in first["tokens"]:
+        logits = plain.forward(w, cfg, seq)[-1]
+        top2 = torch.topk(logits, 2).values
+        if float(top2[0] - top2[1]) > 1e-3:         # a near tie may fall either way
+            assert int(torch.argmax(logits)) == t, len(seq)
+        seq.append(t)
