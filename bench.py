@@ -17,6 +17,9 @@ the same sizes against the plain implementation of tests/plain (float64): the la
 error of the logits of a 512-token prompt's last place and of 8 decoded places.
 Every decode step reads all weights (8 GB) and the live sequences' cache, far more than
 the 126 MB L2, so nothing is flushed between steps.
+
+``--design kadodra`` measures another design instead (see run_design): prompt and decode rates and
+the device time of every stage of a layer at real layer sizes, beside the dense model at equal size.
 """
 from __future__ import annotations
 
