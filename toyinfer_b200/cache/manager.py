@@ -5,7 +5,7 @@ Every schedule entry of the model that owns memory says what it needs
 (parts.base.KVRequest or StateRequest).  Entries with the same key/value needs
 (kv heads, head size, window) form a group with storage of its own:
 
-  k, v            [entries, pages + 1, kv_heads, PAGE, head_dim]   engine dtype
+  k, v            [entries, pages + 1, kv_heads, PAGE, head_dim]   engine dtype (v with value_dim elements when given)
   page table      [slots + 1, pages per sequence]                  int32
 
 A sequence's position p lives in row (p mod PAGE) of page ``table[slot][p // PAGE]``.
@@ -74,7 +74,8 @@ class _KVGroup:
         self.pool = PagePool(n_pages)
         shape = (len(entries), n_pages + 1, req.n_kv_heads, PAGE, req.head_dim)
         self.k = torch.zeros(shape, dtype=dtype, device=device)
-        self.v = torch.zeros(shape, dtype=dtype, device=device) if req.values else None
+        # values may differ from keys in size (KVRequest.value_dim)
+        self.v = torch.zeros(shape[:-1] + (req.value_dim or req.head_dim,), dtype=dtype, device=device) if req.values else None
         self.table_host = np.zeros((n_slots + 1, self.pages_per_seq), dtype=np.int32)
         self.table = torch.zeros((n_slots + 1, self.pages_per_seq), dtype=torch.int32, device=device)
         self.slot_pages: Dict[int, List[int]] = {}
@@ -121,7 +122,8 @@ def bytes_per_token(requests: Sequence[Any], dtype: torch.dtype) -> int:
     """Bytes of cache that one position of one sequence takes, over all schedule entries' requests
     (keys and values; fixed-size states do not grow with the length and count nothing here)."""
     elem = torch.empty((), dtype=dtype).element_size()
-    return sum((2 if r.values else 1) * r.n_kv_heads * r.head_dim * elem for r in requests if isinstance(r, KVRequest))
+    return sum((r.head_dim + ((r.value_dim or r.head_dim) if r.values else 0)) * r.n_kv_heads * elem
+               for r in requests if isinstance(r, KVRequest))
 
 
 class CacheManager:
@@ -212,7 +214,7 @@ class CacheManager:
     def bytes(self) -> int:
         n = 0
         for g in self.kv_groups:
-            n += (2 if g.v is not None else 1) * g.k.numel() * g.k.element_size()
+            n += (g.k.numel() + (g.v.numel() if g.v is not None else 0)) * g.k.element_size()
         for t in self.states.values():
             n += t.numel() * t.element_size()
         return n

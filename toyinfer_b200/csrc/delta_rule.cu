@@ -1,0 +1,197 @@
+// The gated delta rule with one decay per key channel, and the per-head gated norm after it.
+//
+// Per head, with a state S [dim, vdim] in float32 that a sequence carries from token to token
+// (zero when the sequence starts), a unit query q and key k [dim], a value v [vdim], a write
+// strength beta and a decay g [dim] per token:
+//     S <- diag(g) S;   e = beta * (v - S^T k);   S <- S + k e^T;   o = S^T q
+// in this order, so that the read-out sees the token's own write.  Query and key arrive unnormalised
+// (after their short convolution and silu) and are made unit vectors here, x / sqrt(sum x^2 + 1e-6),
+// the query also times dim^-1/2.  The decay comes as the logit l of a low-rank projection:
+// g = exp(-rate_h * softplus(l + dt)), rate_h = exp(A_h) made once.  beta = sigmoid of its logit.
+// Value head h reads query/key head h / (heads / qk_heads).  Everything of the recurrence is 32-bit.
+//
+// delta_rule_scan: a sequence's new tokens are scanned in order from the state in its slot, which
+// is updated in place: whole prompts, single tokens and anything between are one kernel.  Grid
+// (heads * column groups, sequences): a thread owns one column of S (dim registers) and needs no
+// other thread's work; q, k and g of a run of tokens are staged in shared memory, where a warp
+// per token makes them ready.
+//
+// head_gated_rmsnorm: y = o / rms(o) * w * sigmoid(gate) per token and head over vdim, w [vdim]
+// shared by the heads.
+#include "common.cuh"
+
+#include <type_traits>
+
+namespace {
+
+constexpr int DR_TOK = 16;       // tokens staged at a time
+
+__device__ __forceinline__ float softplus_f(float z) { return z > 20.f ? z : log1pf(expf(z)); }
+
+template <typename T, int MAXD>
+__global__ void delta_rule_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v,
+                                       long long q_stride, long long k_stride, long long v_stride,
+                                       const float* __restrict__ decay_logit, const float* __restrict__ dt_bias,
+                                       const float* __restrict__ rate, const T* __restrict__ beta_logit, long long beta_stride,
+                                       float* __restrict__ o, float* __restrict__ state, long long slot_stride,
+                                       const int* __restrict__ cu_new, const int* __restrict__ seq_slot,
+                                       int n_heads, int qk_heads, int dim, int vdim, int groups) {
+    ti_pdl_trigger();
+    extern __shared__ float sm[];        // q, k, g: [DR_TOK][dim] each; beta: [DR_TOK]
+    ti_pdl_sync();
+    q = ti_dependent(q); k = ti_dependent(k); v = ti_dependent(v);
+    decay_logit = ti_dependent(decay_logit); beta_logit = ti_dependent(beta_logit);
+    float* qs = sm;
+    float* ks = qs + DR_TOK * dim;
+    float* gs = ks + DR_TOK * dim;
+    float* bs = gs + DR_TOK * dim;
+    const int h = blockIdx.x / groups, g = blockIdx.x - h * groups;
+    const int b = blockIdx.y;
+    const int tok0 = cu_new[b], n = cu_new[b + 1] - tok0;
+    if (n <= 0) return;
+    const int hq = h / (n_heads / qk_heads);
+    const int col = g * blockDim.x + threadIdx.x;
+    const bool live = col < vdim;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+    const float rt = rate[h], q_scale = rsqrtf((float)dim);
+    float S[MAXD];
+    float* srow = state + (size_t)seq_slot[b] * slot_stride + (size_t)h * dim * vdim;
+#pragma unroll
+    for (int i = 0; i < MAXD; i++) S[i] = (live && i < dim) ? srow[(size_t)i * vdim + col] : 0.f;
+    for (int t0 = 0; t0 < n; t0 += DR_TOK) {
+        const int nt = min(DR_TOK, n - t0);
+        __syncthreads();
+        for (int tt = warp; tt < nt; tt += n_warps) {
+            const size_t tok = (size_t)(tok0 + t0 + tt);
+            float sq = 0.f, sk = 0.f;
+            for (int i = lane; i < dim; i += 32) {
+                const float qv = to_f32(q[tok * q_stride + (size_t)hq * dim + i]);
+                const float kv = to_f32(k[tok * k_stride + (size_t)hq * dim + i]);
+                qs[tt * dim + i] = qv;
+                ks[tt * dim + i] = kv;
+                sq = fmaf(qv, qv, sq);
+                sk = fmaf(kv, kv, sk);
+                const float l = decay_logit[tok * ((size_t)n_heads * dim) + (size_t)h * dim + i] + dt_bias[(size_t)h * dim + i];
+                gs[tt * dim + i] = expf(-rt * softplus_f(l));
+            }
+            sq = warp_sum(sq);
+            sk = warp_sum(sk);
+            const float iq = rsqrtf(sq + 1e-6f) * q_scale, ik = rsqrtf(sk + 1e-6f);
+            for (int i = lane; i < dim; i += 32) {       // a lane rescales what it wrote itself
+                qs[tt * dim + i] *= iq;
+                ks[tt * dim + i] *= ik;
+            }
+            if (lane == 0) bs[tt] = 1.0f / (1.0f + expf(-to_f32(beta_logit[tok * beta_stride + h])));
+        }
+        __syncthreads();
+        if (live) {
+            for (int tt = 0; tt < nt; tt++) {
+                const size_t tok = (size_t)(tok0 + t0 + tt);
+                const float vv = to_f32(v[tok * v_stride + (size_t)h * vdim + col]);
+                const float* kr = ks + tt * dim;
+                const float* qr = qs + tt * dim;
+                const float* gr = gs + tt * dim;
+                float dot = 0.f;
+#pragma unroll
+                for (int i = 0; i < MAXD; i++) {
+                    if (i < dim) {
+                        S[i] *= gr[i];
+                        dot = fmaf(S[i], kr[i], dot);
+                    }
+                }
+                const float e = bs[tt] * (vv - dot);
+                float acc = 0.f;
+#pragma unroll
+                for (int i = 0; i < MAXD; i++) {
+                    if (i < dim) {
+                        S[i] = fmaf(kr[i], e, S[i]);
+                        acc = fmaf(S[i], qr[i], acc);
+                    }
+                }
+                o[tok * ((size_t)n_heads * vdim) + (size_t)h * vdim + col] = acc;
+            }
+        }
+    }
+    if (live) {
+#pragma unroll
+        for (int i = 0; i < MAXD; i++)
+            if (i < dim) srow[(size_t)i * vdim + col] = S[i];
+    }
+}
+
+// one warp per (token, head)
+template <typename T>
+__global__ void head_gated_rmsnorm_kernel(const float* __restrict__ o, const T* __restrict__ gate, long long gate_stride,
+                                          const float* __restrict__ w, T* __restrict__ out, long long rows, int n_heads, int vdim,
+                                          float eps) {
+    ti_pdl_trigger();
+    ti_pdl_sync();
+    o = ti_dependent(o); gate = ti_dependent(gate);
+    const long long r = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (r >= rows) return;
+    const int lane = threadIdx.x & 31;
+    const long long m = r / n_heads;
+    const int h = (int)(r - m * n_heads);
+    const float* orow = o + (size_t)r * vdim;
+    float ss = 0.f;
+    for (int i = lane; i < vdim; i += 32) ss = fmaf(orow[i], orow[i], ss);
+    ss = warp_sum(ss);
+    const float inv = rsqrtf(ss / (float)vdim + eps);
+    for (int i = lane; i < vdim; i += 32) {
+        const float gl = to_f32(gate[(size_t)m * gate_stride + (size_t)h * vdim + i]);
+        out[(size_t)r * vdim + i] = from_f32<T>(orow[i] * inv * w[i] / (1.0f + expf(-gl)));
+    }
+}
+
+template <typename F>
+int dispatch_dim(int dim, F&& f) {
+    if (dim <= 32) return f(std::integral_constant<int, 32>());
+    if (dim <= 64) return f(std::integral_constant<int, 64>());
+    return f(std::integral_constant<int, 128>());
+}
+
+}  // namespace
+
+// q, k: [M, qk_heads, dim] and v: [M, heads, vdim] of the engine's type (row strides given, heads dense); decay_logit:
+// float32 [M, heads * dim]; dt_bias: float32 [heads * dim]; rate: float32 [heads]; beta_logit: [M, heads] (row stride
+// given); o: float32 [M, heads * vdim]; state: float32, slot s at state + s * slot_stride holds [heads, dim, vdim].
+extern "C" int ti_delta_rule_scan(const void* q, const void* k, const void* v, long long q_stride, long long k_stride,
+                                  long long v_stride, const float* decay_logit, const float* dt_bias, const float* rate,
+                                  const void* beta_logit, long long beta_stride, float* o, float* state, long long slot_stride,
+                                  const int* cu_new, const int* seq_slot, int n_seq, int n_heads, int qk_heads, int dim,
+                                  int vdim, int dtype, cudaStream_t stream) {
+    if (n_seq == 0) return 0;
+    TI_REQUIRE(n_seq > 0 && n_seq <= 65535 && n_heads > 0 && qk_heads > 0 && n_heads % qk_heads == 0 && dim > 0 && vdim > 0,
+               "delta_rule_scan: bad sizes");
+    TI_REQUIRE(dim <= 128, "delta_rule: heads of %d query/key elements are not supported (up to 128)", dim);
+    const int threads = vdim <= 32 ? 32 : vdim <= 64 ? 64 : 128, groups = (vdim + threads - 1) / threads;
+    const size_t smem = (size_t)(3 * DR_TOK * dim + DR_TOK) * sizeof(float);
+    return ti_dispatch_dtype(dtype, [&](auto t) -> int {
+        using T = decltype(t);
+        return dispatch_dim(dim, [&](auto md) -> int {
+            constexpr int MAXD = decltype(md)::value;
+            TI_CUDA(ti_launch(delta_rule_scan_kernel<T, MAXD>, dim3(n_heads * groups, n_seq), dim3(threads), smem, stream,
+                              (const T*)q, (const T*)k, (const T*)v, q_stride, k_stride, v_stride, decay_logit, dt_bias, rate,
+                              (const T*)beta_logit, beta_stride, o, state, slot_stride, cu_new, seq_slot, n_heads, qk_heads, dim,
+                              vdim, groups));
+            TI_CHECK_LAUNCH("delta_rule_scan");
+            return 0;
+        });
+    });
+}
+
+// o: float32 [M, heads * vdim]; gate: [M, heads * vdim] of the engine's type with row stride gate_stride; w: float32 [vdim];
+// out: [M, heads * vdim] dense.
+extern "C" int ti_head_gated_rmsnorm(const float* o, const void* gate, long long gate_stride, const float* w, void* out, int M,
+                                     int n_heads, int vdim, float eps, int dtype, cudaStream_t stream) {
+    if (M == 0) return 0;
+    TI_REQUIRE(M > 0 && n_heads > 0 && vdim > 0, "head_gated_rmsnorm: bad sizes");
+    const long long rows = (long long)M * n_heads;
+    return ti_dispatch_dtype(dtype, [&](auto t) -> int {
+        using T = decltype(t);
+        TI_CUDA(ti_launch_class<1>(head_gated_rmsnorm_kernel<T>, dim3((unsigned)((rows + 3) / 4)), dim3(128), 0, stream, o, (const T*)gate,
+                                   gate_stride, w, (T*)out, rows, n_heads, vdim, eps));
+        TI_CHECK_LAUNCH("head_gated_rmsnorm");
+        return 0;
+    });
+}

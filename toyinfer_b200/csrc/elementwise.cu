@@ -312,3 +312,27 @@ extern "C" int ti_swiglu(const void* gu, void* out, int M, int I, int pairs, int
         return 0;
     });
 }
+
+// out[m, n] = y[m, n] + bias[n], rounded once into the engine's type
+template <typename T>
+__global__ void add_row_bias_kernel(const float* __restrict__ y, const float* __restrict__ bias, T* __restrict__ out, int N, long long total) {
+    ti_pdl_trigger();
+    ti_pdl_sync();
+    y = ti_dependent(y);
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x)
+        out[i] = from_f32<T>(y[i] + bias[i % N]);
+}
+
+// y: float32 [M, N] dense (a product's 32-bit result); bias: float32 [N]; out: [M, N] of the engine's type.
+extern "C" int ti_add_row_bias(const float* y, const float* bias, void* out, int M, int N, int dtype, cudaStream_t stream) {
+    if (M == 0) return 0;
+    TI_REQUIRE(M > 0 && N > 0, "add_row_bias: bad sizes");
+    const long long total = (long long)M * N, want = (total + 255) / 256;
+    return ti_dispatch_dtype(dtype, [&](auto t) -> int {
+        using T = decltype(t);
+        TI_CUDA(ti_launch_class<1>(add_row_bias_kernel<T>, dim3((unsigned)(want < 148 * 16 ? want : 148 * 16)), dim3(256), 0, stream, y, bias,
+                                   (T*)out, N, total));
+        TI_CHECK_LAUNCH("add_row_bias");
+        return 0;
+    });
+}

@@ -14,7 +14,7 @@ namespace {
 
 template <typename T>
 __global__ void embed_wide_kernel(const T* __restrict__ table, const int* __restrict__ ids, float* __restrict__ out,
-                                  int H, int vocab, float scale) {
+                                  int H, int vocab, float scale, int copies) {
     ti_pdl_trigger();
     ti_pdl_sync();
     ids = ti_dependent(ids);
@@ -22,7 +22,10 @@ __global__ void embed_wide_kernel(const T* __restrict__ table, const int* __rest
     const int id = ids[m];
     const bool ok = id >= 0 && id < vocab;
     const T* src = table + (size_t)(ok ? id : 0) * H;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) out[(size_t)m * H + i] = ok ? to_f32(src[i]) * scale : 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        const float x = ok ? to_f32(src[i]) * scale : 0.f;
+        for (int c = 0; c < copies; c++) out[((size_t)m * copies + c) * H + i] = x;
+    }
 }
 
 // One block per output row.  W: type of the norm weight (float or T).
@@ -67,13 +70,14 @@ __global__ void add_norm_wide_kernel(float* __restrict__ h, const T* __restrict_
 
 }  // namespace
 
+// out: float32 [M, copies, H]: every token's row `copies` times over (the streams of a model with several).
 extern "C" int ti_embed_wide(const void* table, const int* ids, float* out, int M, int H, int vocab, float scale,
-                             int dtype, cudaStream_t stream) {
+                             int copies, int dtype, cudaStream_t stream) {
     if (M == 0) return 0;
-    TI_REQUIRE(M > 0 && H > 0 && vocab > 0, "embed_wide: bad sizes M=%d H=%d vocab=%d", M, H, vocab);
+    TI_REQUIRE(M > 0 && H > 0 && vocab > 0 && copies >= 1, "embed_wide: bad sizes M=%d H=%d vocab=%d copies=%d", M, H, vocab, copies);
     return ti_dispatch_dtype(dtype, [&](auto t) -> int {
         using T = decltype(t);
-        TI_CUDA(ti_launch_class<1>(embed_wide_kernel<T>, dim3(M), dim3(128), 0, stream, (const T*)table, ids, out, H, vocab, scale));
+        TI_CUDA(ti_launch_class<1>(embed_wide_kernel<T>, dim3(M), dim3(128), 0, stream, (const T*)table, ids, out, H, vocab, scale, copies));
         TI_CHECK_LAUNCH("embed_wide");
         return 0;
     });

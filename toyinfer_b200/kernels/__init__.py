@@ -255,6 +255,23 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
     return out
 
 
+def linear_bias(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor]) -> torch.Tensor:
+    """x[M, K] times w[N, K] transposed plus bias (float32 [N]) -> [M, N] in x's type: the product's 32-bit result takes
+    the bias before it is rounded.  Without a bias this is ``linear``."""
+    if bias is None:
+        return linear(x, w)
+    y = linear(x, w, out_dtype=torch.float32)
+    M, N = y.shape
+    if bias.dtype != torch.float32 or bias.shape != (N,) or not bias.is_contiguous() or not bias.is_cuda:
+        raise KernelError(f"linear_bias: the bias must be dense float32 [{N}] on the device")
+    from .lib import declare
+    out = torch.empty((M, N), dtype=w.dtype, device=y.device)
+    fn = declare("ti_add_row_bias", [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int,
+                                     ctypes.c_void_p])
+    _call(fn, _ptr(y), _ptr(bias), _ptr(out), M, N, _code(out, "linear_bias"), _stream())
+    return out
+
+
 def swiglu(gu: torch.Tensor, pairs: bool = False) -> torch.Tensor:
     """up * gate / (1 + exp(-gate)).  gu[M, 2*I] holds gate in its first I columns and up in
     the rest, or with ``pairs`` gate_i and up_i side by side."""

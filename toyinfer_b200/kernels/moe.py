@@ -94,3 +94,81 @@ def experts_ffn(x: torch.Tensor, perm: torch.Tensor, off: torch.Tensor, w_gate_u
     out = torch.empty((M, H), dtype=x.dtype, device=x.device)
     _call(_fn("ti_moe_combine", [P, P, I, I, I, I, P]), _ptr(z), _ptr(out), M, H, top, code, _stream())
     return out
+
+
+def route_topk(z: torch.Tensor, n_experts: int, top: int):
+    """z float32 [M, >= experts] (rows may be strided; the first ``n_experts`` columns are the router's logits) ->
+    (perm int32 [M * top], off int32 [experts + 1], score float32 [M * top], score squared): every token's ``top``
+    experts by sigmoid(z), the (token, choice) pairs grouped by expert (csrc/moe_router.cu)."""
+    _need_cuda(z, what="moe_route_topk")
+    if z.dtype != torch.float32 or z.dim() != 2 or z.stride(1) != 1 or z.shape[1] < n_experts:
+        raise KernelError("moe_route_topk: the router's logits must be float32 [tokens, experts] with dense rows")
+    M = z.shape[0]
+    dev = z.device
+    perm = torch.empty(M * top, dtype=torch.int32, device=dev)
+    off = torch.empty(n_experts + 1, dtype=torch.int32, device=dev)
+    scratch = torch.empty(M * top, dtype=torch.int32, device=dev)
+    score = torch.empty(M * top, dtype=torch.float32, device=dev)
+    score2 = torch.empty(M * top, dtype=torch.float32, device=dev)
+    _call(_fn("ti_moe_route_topk", [P, L, I, I, I, P, P, P, P, P, P]), _ptr(z), z.stride(0), int(n_experts), int(top), M, _ptr(perm),
+          _ptr(off), _ptr(scratch), _ptr(score), _ptr(score2), _stream())
+    return perm, off, score, score2
+
+
+def experts_relu2(x: torch.Tensor, perm: torch.Tensor, off: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, top: int):
+    """Every pair's Wdown relu(Wup x)^2 with its expert's matrices: x [M, H]; w_up [experts, ff, H]; w_down [experts, H, ff].
+    Returns (z, place_of_pair): pair p's row is z[place_of_pair[p]], or z[p] when place_of_pair is None.  The same two
+    ways as ``experts_ffn``: padded groups on tcgen05 for many tokens per expert, the grouped tiles otherwise."""
+    _need_cuda(x, perm, off, w_up, w_down, what="moe")
+    M, H = x.shape
+    E, ff, H2 = w_up.shape
+    if H2 != H or w_down.shape != (E, H, ff) or x.stride(1) != 1:
+        raise KernelError("moe: the experts' matrices do not fit the tokens")
+    for t in (w_up, w_down):
+        if t.dtype != x.dtype or not t.is_contiguous():
+            raise KernelError("moe: the experts' matrices must be dense and of the tokens' dtype")
+    Pn = M * top
+    code = _code(x, "moe")
+    dev = x.device
+    if (x.dtype == torch.bfloat16 and H % 8 == 0 and ff % 8 == 0 and Pn >= TC_MIN_GROUP * E and x.stride(0) % 8 == 0
+            and x.data_ptr() % 16 == 0):
+        rows = (Pn + 127 * E + 127) // 128 * 128
+        pad_src = torch.empty(rows, dtype=torch.int32, device=dev)
+        pad_of_pair = torch.empty(Pn, dtype=torch.int32, device=dev)
+        tile_group = torch.empty(rows // 128, dtype=torch.int32, device=dev)
+        _call(_fn("ti_moe_pad_plan", [P, P, I, I, I, I, P, P, P, P]), _ptr(perm), _ptr(off), E, Pn, top, rows, _ptr(pad_src),
+              _ptr(pad_of_pair), _ptr(tile_group), _stream())
+        xs = torch.empty((rows, H), dtype=x.dtype, device=dev)
+        _call(_fn("ti_moe_gather_rows", [P, L, P, P, I, I, I, P]), _ptr(x), x.stride(0), _ptr(pad_src), _ptr(xs), rows, H, code, _stream())
+        grouped = _fn("ti_linear_grouped_tc", [P, P, P, P, I, I, I, I, L, P])
+        u = torch.empty((rows, ff), dtype=x.dtype, device=dev)
+        _call(grouped, _ptr(xs), _ptr(w_up), _ptr(u), _ptr(tile_group), rows, E, ff, H, ff, _stream())
+        y = relu2(u)
+        z = torch.empty((rows, H), dtype=x.dtype, device=dev)
+        _call(grouped, _ptr(y), _ptr(w_down), _ptr(z), _ptr(tile_group), rows, E, H, ff, H, _stream())
+        return z, pad_of_pair
+    fn = _fn("ti_moe_grouped", [P, L, P, P, P, L, P, P, I, I, I, I, I, I, I, I, F, F, F, L, I, P])
+    u = torch.empty((Pn, ff), dtype=x.dtype, device=dev)
+    _call(fn, _ptr(x), x.stride(0), _ptr(w_up), None, _ptr(u), ff, _ptr(perm), _ptr(off), E, Pn, ff, H, top, 1, 0, 0,
+          1.0, 0.0, 0.0, 0, code, _stream())
+    y = relu2(u)
+    z = torch.empty((Pn, H), dtype=x.dtype, device=dev)
+    _call(fn, _ptr(y), ff, _ptr(w_down), None, _ptr(z), H, _ptr(perm), _ptr(off), E, Pn, H, ff, top, 0, 1, 0,
+          1.0, 0.0, 0.0, 0, code, _stream())
+    return z, None
+
+
+def combine_gated(z: torch.Tensor, place_of_pair, pair_w, shared_out, gate_logit, M: int, top: int) -> torch.Tensor:
+    """out[m] = sum_j pair_w[m * top + j] * z[place of that pair] + sigmoid(gate_logit[m]) * shared_out[m].  z [places, H];
+    pair_w float32 [M * top] or None; shared_out [M, H] or None; gate_logit float32 [M] (may be strided) or None."""
+    _need_cuda(z, place_of_pair, pair_w, shared_out, gate_logit, what="moe_combine_gated")
+    H = z.shape[1]
+    if not z.is_contiguous() or (shared_out is not None and (tuple(shared_out.shape) != (M, H) or shared_out.dtype != z.dtype
+                                                             or not shared_out.is_contiguous())):
+        raise KernelError("moe_combine_gated: the outputs must be dense and of one type")
+    if gate_logit is not None and (gate_logit.dtype != torch.float32 or gate_logit.dim() != 1 or gate_logit.shape[0] != M):
+        raise KernelError("moe_combine_gated: the gate's logits must be float32 [tokens]")
+    out = torch.empty((M, H), dtype=z.dtype, device=z.device)
+    _call(_fn("ti_moe_combine_gated", [P, P, P, P, P, L, P, I, I, I, I, P]), _ptr(z), _ptr(place_of_pair), _ptr(pair_w), _ptr(shared_out),
+          _ptr(gate_logit), gate_logit.stride(0) if gate_logit is not None else 0, _ptr(out), M, H, int(top), _code(z, "moe"), _stream())
+    return out

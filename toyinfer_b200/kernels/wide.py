@@ -35,14 +35,14 @@ def pending_terms(delta: Pending) -> Tuple[Optional[torch.Tensor], Optional[torc
     return terms
 
 
-def embed_wide(table: torch.Tensor, ids: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
-    """float32 out[m] = table[ids[m]] * scale."""
+def embed_wide(table: torch.Tensor, ids: torch.Tensor, scale: float = 1.0, copies: int = 1) -> torch.Tensor:
+    """float32 out[m] = table[ids[m]] * scale, ``copies`` times side by side ([M, copies * H])."""
     _need_cuda(table, ids, what="embed_wide")
     _i32(ids, "embed_wide ids")
     V, H = table.shape
-    out = torch.empty((ids.numel(), H), dtype=torch.float32, device=table.device)
-    _call(_fn("ti_embed_wide", [P, P, P, I, I, I, F, I, P]), _ptr(table), _ptr(ids), _ptr(out), ids.numel(), H, V,
-          float(scale), _code(table, "embed_wide"), _stream())
+    out = torch.empty((ids.numel(), int(copies) * H), dtype=torch.float32, device=table.device)
+    _call(_fn("ti_embed_wide", [P, P, P, I, I, I, F, I, I, P]), _ptr(table), _ptr(ids), _ptr(out), ids.numel(), H, V,
+          float(scale), int(copies), _code(table, "embed_wide"), _stream())
     return out
 
 

@@ -18,7 +18,8 @@ from .base import (
     registered_parts,
     unregister_part,
 )
-from . import norms, rope, attention, latent_attention, lightning, mlp, block, parallel_block, ends  # noqa: F401  (registration)
+from . import (norms, rope, attention, latent_attention, lightning, mlp, block, parallel_block, ends,  # noqa: F401  (registration)
+               hyper_block, rglru, biased_attention, channel_delta)
 from .model import DecoderModel, LayerSpec, ModelSpec, ScheduleEntry
 
 __all__ = [

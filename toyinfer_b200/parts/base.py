@@ -61,8 +61,10 @@ class ParamSpec:
 
     role: "matrix" (follows the engine's dtype), "norm" (follows the engine's
     dtype, but a tensor stored in 32-bit stays 32-bit), "int_table" (int32).
-    init: "normal" N(0, std), "one_plus_normal" 1 + N(0, std), "zeros", "ones"; for an integer table
+    init: "normal" N(mean, std), "one_plus_normal" 1 + N(0, std), "zeros", "ones"; for an integer table
     "distinct_below": every row holds different integers drawn from 0 .. high - 1.
+    free: dimensions whose size the checkpoint decides (``shape`` holds the size that random weights are drawn with);
+    the part looks at the tensor it is bound to.
     """
 
     shape: Tuple[int, ...]
@@ -70,6 +72,8 @@ class ParamSpec:
     init: str = "normal"
     std: float = 0.02
     high: int = 0
+    mean: float = 0.0
+    free: Tuple[int, ...] = ()
 
 
 @dataclass(frozen=True)
@@ -121,6 +125,7 @@ class KVRequest:
     head_dim: int
     window: int = 0
     values: bool = True        # False: one row per position and kv head only (a mixer that reads its values out of the same row)
+    value_dim: int = 0         # elements of a value when they differ from a key's (0: head_dim)
 
 
 @dataclass(frozen=True)

@@ -23,10 +23,13 @@ from .base import BuildContext, Embedding, Head, ParamSpec, PartSpec, build_part
 
 class TokenEmbedding(Embedding):
     def __init__(self, ctx: BuildContext, prefix: str, vocab_size: int, scale: float = 1.0,
-                 name: str = "model.embed_tokens.weight", wide: bool = False):
+                 name: str = "model.embed_tokens.weight", wide: bool = False, copies: int = 1):
         self.vocab_size, self.hidden = int(vocab_size), ctx.hidden_size
         self.scale = float(scale)
         self.wide = bool(wide)          # the rows come out as a float32 stream whatever the table's type
+        self.copies = int(copies)       # ... and that many times side by side (a model with several residual streams)
+        if self.copies < 1 or (self.copies > 1 and not self.wide):
+            raise ValueError("several copies of the embedding's rows need a float32 stream (wide=True)")
         self.name = prefix + name
         self.weight: Optional[torch.Tensor] = None
 
@@ -41,7 +44,7 @@ class TokenEmbedding(Embedding):
 
     def forward(self, token_ids: torch.Tensor) -> torch.Tensor:
         if self.wide:
-            return wide.embed_wide(self.weight, token_ids, self.scale)
+            return wide.embed_wide(self.weight, token_ids, self.scale, self.copies)
         return K.embed(self.weight, token_ids, self.scale)
 
     def rows(self, token_ids: torch.Tensor) -> torch.Tensor:

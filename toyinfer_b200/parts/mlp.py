@@ -133,3 +133,73 @@ class TableMoE(FeedForward):
 
 register_part("feed_forward", "relu2", SquaredReLU)
 register_part("feed_forward", "table_moe", TableMoE)
+
+
+class ScoredMoE(FeedForward):
+    """Mixture of experts with independent scores: z = Wr x (float32), s = sigmoid(z); the ``top`` experts with the largest
+    scores run, each on the token's row times its score (not renormalised): y = sum_e Wdown_e relu(Wup_e (s_e x))^2.  A shared
+    expert of the same form (its own width) may run for every token, times sigmoid(wg . x).  No biases.
+
+    Since s > 0 the scaled input is the same as s^2 on the expert's output: the products run on x, grouped by expert on
+    the device (kernels/moe.py), and the sum at the end applies the squares.  The router's matrix and the shared gate's
+    row are one product with a float32 result."""
+
+    captures_start = True
+
+    def __init__(self, ctx: BuildContext, prefix: str, n_experts: int, top: int, intermediate_size: int,
+                 shared_size: int = 0, names: Optional[Dict[str, str]] = None):
+        self.hidden = ctx.hidden_size
+        self.n_experts, self.top, self.inter, self.shared = int(n_experts), int(top), int(intermediate_size), int(shared_size)
+        if not (1 <= self.top <= self.n_experts):
+            raise ValueError(f"moe at {prefix!r}: {self.top} of {self.n_experts} experts per token")
+        n = {"expert": "e{}.", "up": "up", "down": "down", "router": "router", "shared": "shared.", "shared_gate": "shared.sg"}
+        n.update(names or {})
+        self.prefix, self.n = prefix, n
+        self.w_up = self.w_down = self.w_router = self.ws_up = self.ws_down = None
+
+    def _name(self, e: int, which: str) -> str:
+        return self.prefix + self.n["expert"].format(e) + self.n[which]
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        s: Dict[str, ParamSpec] = {}
+        for e in range(self.n_experts):
+            s[self._name(e, "up")] = ParamSpec((self.inter, self.hidden), std=0.05)
+            s[self._name(e, "down")] = ParamSpec((self.hidden, self.inter), std=0.05)
+        s[self.prefix + self.n["router"]] = ParamSpec((self.n_experts, self.hidden), std=0.1)
+        if self.shared:
+            p = self.prefix + self.n["shared"]
+            s[p + self.n["up"]] = ParamSpec((self.shared, self.hidden), std=0.05)
+            s[p + self.n["down"]] = ParamSpec((self.hidden, self.shared), std=0.05)
+            s[self.prefix + self.n["shared_gate"]] = ParamSpec((1, self.hidden), std=0.1)
+        return s
+
+    def check_kernels(self, dtype) -> None:
+        if self.top > 16:
+            raise K.KernelError(f"moe: {self.top} experts per token are not supported (up to 16)")
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        E = range(self.n_experts)
+        self.w_up = torch.stack([tensors.pop(self._name(e, "up")) for e in E]).contiguous()
+        self.w_down = torch.stack([tensors.pop(self._name(e, "down")) for e in E]).contiguous()
+        rows = [tensors.pop(self.prefix + self.n["router"])]
+        if self.shared:
+            p = self.prefix + self.n["shared"]
+            self.ws_up = tensors.pop(p + self.n["up"]).contiguous()
+            self.ws_down = tensors.pop(p + self.n["down"]).contiguous()
+            rows.append(tensors.pop(self.prefix + self.n["shared_gate"]).reshape(1, self.hidden))
+        self.w_router = torch.cat(rows, dim=0).contiguous()
+
+    def forward(self, x, batch) -> torch.Tensor:
+        from ..kernels import moe as KM
+        M = x.shape[0]
+        z = K.linear(x, self.w_router, out_dtype=torch.float32)            # [M, experts (+ 1)]
+        perm, off, _, score2 = KM.route_topk(z, self.n_experts, self.top)
+        y, place = KM.experts_relu2(x, perm, off, self.w_up, self.w_down, self.top)
+        shared = gate = None
+        if self.shared:
+            shared = K.linear(KM.relu2(K.linear(x, self.ws_up)), self.ws_down)
+            gate = z[:, self.n_experts]
+        return KM.combine_gated(y, place, score2, shared, gate, M, self.top)
+
+
+register_part("feed_forward", "scored_moe", ScoredMoE)

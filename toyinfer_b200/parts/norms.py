@@ -63,3 +63,44 @@ class RMSNorm(Norm):
 
 
 register_part("norm", "rmsnorm", RMSNorm)
+
+
+class StreamRMSNorm(Norm):
+    """The norm that reads several float32 residual streams (kernels/hyper.py): y = rms(u) * w with
+    u = sum_s read[s] X_s, after the update a sublayer left pending on X has been applied.  ``one_plus``: the stored
+    weight lies around zero and 1 + w multiplies (formed once, in float32).  The weight is float32 whatever the
+    engine's type; the normed rows come out in the engine's type."""
+
+    def __init__(self, ctx: BuildContext, prefix: str, size: int, eps: float, name: str = "weight", streams: int = 1,
+                 one_plus: bool = False):
+        self.size, self.eps, self.streams = int(size), float(eps), int(streams)
+        self.one_plus = bool(one_plus)
+        self.weight_name = prefix + name
+        self.weight: Optional[torch.Tensor] = None
+        self.out_dtype = ctx.dtype
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        return {self.weight_name: ParamSpec((self.size,), role="norm", init="normal" if self.one_plus else "one_plus_normal")}
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        w = tensors.pop(self.weight_name).to(torch.float32)
+        self.weight = (1.0 + w if self.one_plus else w).contiguous()
+
+    def read_forward(self, X: torch.Tensor, pending, read: Optional[torch.Tensor]) -> torch.Tensor:
+        """X takes ``pending`` (a kernels.hyper.StreamUpdate or None) in place; returns the norm of the streams read with ``read``."""
+        from ..kernels import hyper
+        return hyper.hyper_norm(X, pending, read, self.weight, self.eps, self.out_dtype, self.streams)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return self.read_forward(x, None, None)
+
+    def add_forward(self, h: torch.Tensor, delta) -> torch.Tensor:
+        return self.read_forward(h, delta, None)
+
+    def gather_add_forward(self, h: torch.Tensor, delta, rows: torch.Tensor) -> torch.Tensor:
+        """The norm of the sum of the streams of the rows ``rows``, the pending update included; h stays as it is."""
+        from ..kernels import hyper
+        return hyper.hyper_norm(h, delta, None, self.weight, self.eps, self.out_dtype, self.streams, rows=rows)
+
+
+register_part("norm", "stream_rmsnorm", StreamRMSNorm)

@@ -70,7 +70,8 @@ def load_parameters(
                 missing.append(name)
                 continue
             e = f.entries[name]
-            if tuple(e.shape) != tuple(spec.shape):
+            if len(e.shape) != len(spec.shape) or any(a != b for i, (a, b) in enumerate(zip(e.shape, spec.shape))
+                                                      if i not in spec.free):
                 wrong.append(f"{name}: shape {list(e.shape)} in the file, {list(spec.shape)} expected")
                 continue
             _, err = _target_dtype(name, spec, e.dtype, dtype)

@@ -42,7 +42,7 @@ def draw(spec: ParamSpec, name: str, seed: int, device="cpu") -> torch.Tensor:
     if spec.init == "ones":
         return torch.ones(spec.shape, dtype=torch.float32, device=device)
     t = torch.empty(spec.shape, dtype=torch.float32, device=device)
-    t.normal_(0.0, spec.std, generator=g)
+    t.normal_(spec.mean, spec.std, generator=g)
     if spec.init == "one_plus_normal":
         t += 1.0
     elif spec.init != "normal":
