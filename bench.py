@@ -18,7 +18,7 @@ error of the logits of a 512-token prompt's last place and of 8 decoded places.
 Every decode step reads all weights (8 GB) and the live sequences' cache, far more than
 the 126 MB L2, so nothing is flushed between steps.
 
-``--design kadodra`` measures another design instead (see run_design): prompt and decode rates and
+``--design kadodra`` (or ``tusasun``) measures another design instead (see run_design): prompt and decode rates and
 the device time of every stage of a layer at real layer sizes, beside the dense model at equal size.
 """
 from __future__ import annotations
@@ -471,6 +471,23 @@ def _kadodra_config(width, heads, layers, kind, vocab=32000):
             "layers": [json.loads(json.dumps(layer)) for _ in range(layers)], "max_positions": 8192}
 
 
+def _tusasun_config(width, heads, layers, kind, vocab=32000):
+    """``layers`` equal layers of one kind of mixer, "attention" (soft cap, distance table, 4 query heads per kv head), "rglru"
+    (a recurrent block as wide as the model, a gate block per 128 channels) or "delta" (gated delta rule, heads of 128), each
+    over four residual streams and before sixteen squared-ReLU experts of the model's width, two per token, and a shared one."""
+    if kind == "attention":
+        layer = {"type": "attention", "mixer": {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+                                                "softcap": 50.0, "bias_max": 4096, "bias_rows": 32}}
+    elif kind == "rglru":
+        layer = {"type": "rglru", "mixer": {"width": width, "blocks": heads, "conv": 4}}
+    else:
+        layer = {"type": "channel_delta", "mixer": {"heads": heads, "kv_heads": heads, "dim": 128, "vdim": 128, "conv": 4,
+                                                    "decay_rank": 64, "gate_rank": 64}}
+    layer["mlp"] = {"kind": "moe", "expert": {"ff": width}, "router": {"experts": 16, "top": 2}, "shared": {"ff": width}}
+    return {"architecture": "Tusasun", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "streams": 4,
+            "layers": [json.loads(json.dumps(layer)) for _ in range(layers)], "max_positions": 8192}
+
+
 def _qwen3_like(width, heads, layers, vocab=32000):
     """The dense model of the same width, head count and layers; its three feed-forward matrices of 8/3 width hold what the
     other design's two of 4 width (or its two active experts of three matrices each, 6 width... the nearest round size) hold."""
@@ -487,13 +504,21 @@ def run_design(name: str, widths, layers: int, tokens: int, batch: int, context:
     import torch
     from toyinfer_b200.engine import Engine
     from toyinfer_b200.tracing import Tracer
-    if name != "kadodra":
-        raise SystemExit(f"bench.py: unknown design {name!r} (kadodra)")
+    if name not in ("kadodra", "tusasun"):
+        raise SystemExit(f"bench.py: unknown design {name!r} (kadodra, tusasun)")
     for width in widths:
         heads = width // 128
-        models = [("kadodra latent+dense", _kadodra_config(width, heads, layers, "latent")),
-                  ("kadodra lightning+experts", _kadodra_config(width, heads, layers, "lightning")),
-                  ("qwen3 dense", _qwen3_like(width, heads, layers))]
+        if name == "kadodra":
+            models = [("kadodra latent+dense", _kadodra_config(width, heads, layers, "latent")),
+                      ("kadodra lightning+experts", _kadodra_config(width, heads, layers, "lightning")),
+                      ("qwen3 dense", _qwen3_like(width, heads, layers))]
+        else:       # its closest relation is the other design with a float32 stream, a state per sequence and experts
+            models = [("tusasun attention+experts", _tusasun_config(width, heads, layers, "attention")),
+                      ("tusasun rglru+experts", _tusasun_config(width, heads, layers, "rglru")),
+                      ("tusasun delta+experts", _tusasun_config(width, heads, layers, "delta")),
+                      ("kadodra lightning+experts", _kadodra_config(width, heads, layers, "lightning")),
+                      ("kadodra latent+dense", _kadodra_config(width, heads, layers, "latent")),
+                      ("qwen3 dense", _qwen3_like(width, heads, layers))]
         for label, cfg in models:
             kw = dict(seed=0, dtype="bfloat16", max_tokens=batch * (context + 64) + tokens + 64, max_batch=batch, max_seq_len=context + 64)
             sampler = ClockSampler()
@@ -702,7 +727,7 @@ def main() -> int:
                     help="run one of the larger described workloads end to end instead (8B or 32B shape)")
     ap.add_argument("--prompt-steps", default="", help="time one prompt step of each of these lengths instead (comma-separated), "
                     "with --layers layers")
-    ap.add_argument("--design", default="", help="measure another design beside the dense model at equal size instead: kadodra "
+    ap.add_argument("--design", default="", help="measure another design beside its closest relations at equal size instead: kadodra or tusasun "
                     "(with --widths, --layers, --tokens, --batch, --context)")
     ap.add_argument("--widths", default="2048,4096", help="with --design: model widths (heads of 128)")
     ap.add_argument("--tokens", type=int, default=PREFILL_TOKENS, help="with --design: the prompt's tokens")

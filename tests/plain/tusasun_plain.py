@@ -119,22 +119,25 @@ def distance_bucket(d: int, rows: int, far: float) -> int:
 def attention(h: torch.Tensor, w: Dict[str, torch.Tensor], p: str, m: dict, eps: float) -> torch.Tensor:
     T = h.shape[0]
     H, G, dim, vd = int(m["heads"]), int(m["kv_heads"]), int(m["dim"]), int(m["vdim"])
-    scale, cap, far = float(m["scale"]), float(m["softcap"]), float(m["bias_max"])
+    scale, cap, far = float(m["scale"]), m.get("softcap"), m.get("bias_max")          # cap and table are each optional
     h = h.to(F64)
     q = (h @ w[p + "q"].to(F64).T + w[p + "q.b"].to(F64)).view(T, H, dim)
     k = (h @ w[p + "k"].to(F64).T + w[p + "k.b"].to(F64)).view(T, G, dim)
     v = (h @ w[p + "v"].to(F64).T + w[p + "v.b"].to(F64)).view(T, G, vd)
     q = plain_norm(q, w[p + "q.norm"], eps)
     k = plain_norm(k, w[p + "k.norm"], eps)
-    table = w[p + "rel"].to(F64)
-    rows = table.shape[0]
+    table = w[p + "rel"].to(F64) if far else None
     out = torch.zeros(T, H, vd, dtype=F64)
     for t in range(T):
-        bias = torch.stack([table[distance_bucket(t - j, rows, far)] for j in range(t + 1)])      # [t + 1, H]
+        if far:
+            bias = torch.stack([table[distance_bucket(t - j, table.shape[0], float(far))] for j in range(t + 1)])      # [t + 1, H]
         for hh in range(H):
             g = hh // (H // G)
             s = (k[:t + 1, g] @ q[t, hh]) * scale
-            s = cap * torch.tanh(s / cap) + bias[:, hh]
+            if cap:
+                s = float(cap) * torch.tanh(s / float(cap))
+            if far:
+                s = s + bias[:, hh]
             e = torch.exp(s - s.max())
             out[t, hh] = (e / e.sum()) @ v[:t + 1, g]
     return out.reshape(T, H * vd) @ w[p + "o"].to(F64).T + w[p + "o.b"].to(F64)
@@ -189,6 +192,18 @@ def routed_experts(h: torch.Tensor, w: Dict[str, torch.Tensor], p: str, f: dict)
 
 
 # ---------------------------------------------------------------------------
+# streams
+# ---------------------------------------------------------------------------
+def read_streams(X: Sequence[torch.Tensor], a: torch.Tensor) -> torch.Tensor:
+    return sum(a[i].to(F64) * X[i].to(F64) for i in range(len(X)))
+
+
+def write_streams(X: Sequence[torch.Tensor], M: torch.Tensor, b: torch.Tensor, y: torch.Tensor) -> List[torch.Tensor]:
+    n = len(X)
+    return [sum(M[i, j].to(F64) * X[i].to(F64) for i in range(n)) + b[j].to(F64) * y.to(F64) for j in range(n)]
+
+
+# ---------------------------------------------------------------------------
 # the model
 # ---------------------------------------------------------------------------
 def run_order(cfg: dict) -> List[int]:
@@ -219,14 +234,13 @@ def forward(w: Dict[str, torch.Tensor], cfg: dict, ids: Sequence[int], keep_laye
                 a, M, b = (w[f"{p}hc{q}.{s}"].to(F64) for s in ("in", "mix", "out"))
             else:
                 a, M, b = torch.ones(1, dtype=F64), torch.ones(1, 1, dtype=F64), torch.ones(1, dtype=F64)
-            u = sum(a[i] * X[i] for i in range(n))
-            z = one_plus_norm(u, w[f"{p}norm{q}"], eps)
+            z = one_plus_norm(read_streams(X, a), w[f"{p}norm{q}"], eps)
             if kind == "mixer":
                 y = MIXERS[L["type"]](z, w, p + "mix.", L["mixer"], eps)
             else:
                 y = routed_experts(z, w, p + "mlp.", L["mlp"])
             y = y * w[f"{p}ls{q}"].to(F64)
-            X = [sum(M[i, j] * X[i] for i in range(n)) + b[j] * y for j in range(n)]
+            X = write_streams(X, M, b, y)
         sums.append(sum(X).clone())
     x = sum(X)
     logits = one_plus_norm(x, w["final.norm"], eps) @ w["head"].to(F64).T

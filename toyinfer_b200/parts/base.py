@@ -61,7 +61,8 @@ class ParamSpec:
 
     role: "matrix" (follows the engine's dtype), "norm" (follows the engine's
     dtype, but a tensor stored in 32-bit stays 32-bit), "int_table" (int32).
-    init: "normal" N(mean, std), "one_plus_normal" 1 + N(0, std), "zeros", "ones"; for an integer table
+    init: "normal" N(mean, std), "one_plus_normal" 1 + N(0, std), "eye_plus_normal" (a matrix: the identity plus
+    N(mean, std)), "zeros", "ones"; for an integer table
     "distinct_below": every row holds different integers drawn from 0 .. high - 1.
     free: dimensions whose size the checkpoint decides (``shape`` holds the size that random weights are drawn with);
     the part looks at the tensor it is bound to.

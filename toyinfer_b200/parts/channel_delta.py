@@ -90,6 +90,8 @@ class ChannelDeltaAttention(Mixer):
             self.cols.append(at)
             rows.append(p)
             at += p.shape[0]
+        if _up8(at) > at:                    # ... and a token's row of results is a multiple of 8 long
+            rows.append(torch.zeros((_up8(at) - at, self.hidden), dtype=rows[0].dtype, device=rows[0].device))
         self.w_in = torch.cat(rows, dim=0).contiguous()
         self.w_decay = t("decay_out").contiguous()
         self.w_gate = t("gate_out").contiguous()

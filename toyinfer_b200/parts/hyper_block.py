@@ -60,9 +60,10 @@ class HyperBlock(Block):
                 out[self.prefix + self.n[f"scale{q}"]] = ParamSpec((self.hidden,), role="norm", init="normal", mean=0.5, std=0.1)
             if self.connections:
                 c = self.prefix + self.n[f"conn{q}"]
-                out[c + "in"] = ParamSpec((S,), role="norm", init="normal", mean=1.0 / S, std=0.2)
-                out[c + "out"] = ParamSpec((S,), role="norm", init="normal", mean=1.0, std=0.3)
-                out[c + "mix"] = ParamSpec((S, S), role="norm", init="normal", mean=1.0 / S, std=0.3)
+                # (drawn near a plain residual sum: streams that are carried as they are, read evenly, written alike)
+                out[c + "in"] = ParamSpec((S,), role="norm", init="normal", mean=1.0 / S, std=0.1 / S)
+                out[c + "out"] = ParamSpec((S,), role="norm", init="normal", mean=1.0, std=0.2)
+                out[c + "mix"] = ParamSpec((S, S), role="norm", init="eye_plus_normal", std=0.1)
         return out
 
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:

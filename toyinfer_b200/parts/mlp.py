@@ -165,7 +165,7 @@ class ScoredMoE(FeedForward):
         for e in range(self.n_experts):
             s[self._name(e, "up")] = ParamSpec((self.inter, self.hidden), std=0.05)
             s[self._name(e, "down")] = ParamSpec((self.hidden, self.inter), std=0.05)
-        s[self.prefix + self.n["router"]] = ParamSpec((self.n_experts, self.hidden), std=0.1)
+        s[self.prefix + self.n["router"]] = ParamSpec((self.n_experts, self.hidden), std=0.3)
         if self.shared:
             p = self.prefix + self.n["shared"]
             s[p + self.n["up"]] = ParamSpec((self.shared, self.hidden), std=0.05)

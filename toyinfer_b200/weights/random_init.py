@@ -45,7 +45,9 @@ def draw(spec: ParamSpec, name: str, seed: int, device="cpu") -> torch.Tensor:
     t.normal_(spec.mean, spec.std, generator=g)
     if spec.init == "one_plus_normal":
         t += 1.0
-    elif spec.init != "normal":
+    elif spec.init == "eye_plus_normal":
+        t += torch.eye(spec.shape[0], spec.shape[1], dtype=torch.float32, device=device)
+    elif spec.init not in ("normal",):
         raise ValueError(f"{name}: unknown init {spec.init!r}")
     return t
 
