@@ -171,16 +171,22 @@ RGLRU = [dict(width=96, blocks=3, conv=4), dict(width=40, blocks=1, conv=1), dic
 
 
 @pytest.mark.parametrize("dtype", DT)
+@pytest.mark.parametrize("chunked_from", [None, 2])
 @pytest.mark.parametrize("c", RGLRU)
-def test_recurrent_block(dtype, c):
+def test_recurrent_block(dtype, c, chunked_from, monkeypatch):
+    """``chunked_from``: every step that brings a sequence two tokens or more runs the chunked form of the recurrence (chunks
+    of 128 in parallel, a walk over their effects), which otherwise starts at 256."""
+    from toyinfer_b200.kernels import recurrent as KR
     from toyinfer_b200.parts import PartSpec, build_part
+    if chunked_from is not None:
+        monkeypatch.setattr(KR, "RGLRU_CHUNKED_FROM", chunked_from)
     hidden = 56
     m = build_part("mixer", PartSpec("rglru", dict(c)), ctx_for(dtype, hidden), "a.")
 
     def edit(cpu):                  # decays from nearly none to nearly all, so that a lost or doubled state shows
         cpu["a.lam"].copy_(torch.linspace(-6.0, 2.0, c["width"]))
     w = bind_random(m, 3, dtype, edit)
-    xs = inputs([170, 66, 3], hidden, 5, dtype)
+    xs = inputs([300, 129, 3], hidden, 5, dtype)
     wants = [plain.rglru(x.double(), w, "a.", c) for x in xs]
     check_all_schedules(m, xs, wants, dtype)
 
@@ -188,7 +194,11 @@ def test_recurrent_block(dtype, c):
 ATT = [dict(n_heads=4, n_kv_heads=2, dim=24, vdim=40, softcap=30.0, bias_rows=12, bias_max=50.0),
        dict(n_heads=3, n_kv_heads=3, dim=64, vdim=16, softcap=1.5, bias_rows=32, bias_max=400.0),
        dict(n_heads=6, n_kv_heads=1, dim=8, vdim=8, softcap=0.0, bias_rows=0, bias_max=0.0),
-       dict(n_heads=2, n_kv_heads=1, dim=128, vdim=200, softcap=50.0, bias_rows=6, bias_max=9.0)]
+       dict(n_heads=2, n_kv_heads=1, dim=128, vdim=200, softcap=50.0, bias_rows=6, bias_max=9.0),
+       # the two shapes that the tensor-core kernel takes in bfloat16 (keys and values of 64 or of 128)
+       dict(n_heads=4, n_kv_heads=2, dim=64, vdim=64, softcap=20.0, bias_rows=16, bias_max=100.0),
+       dict(n_heads=2, n_kv_heads=1, dim=128, vdim=128, softcap=0.0, bias_rows=8, bias_max=300.0),
+       dict(n_heads=2, n_kv_heads=2, dim=128, vdim=128, softcap=3.0, bias_rows=0, bias_max=0.0)]
 
 
 def att_cfg(c, scale):

@@ -10,15 +10,15 @@
 // query or key has `dim` elements, a value `vdim`.
 //
 // attn_bias_prepare: from the projection's output row [q | k | v]: adds the projections' biases,
-// norms every query and key head (x * rsqrt(mean(x^2) + eps) * w, plain weight), leaves the query
+// norms every query and key head (x * rsqrt(mean(x^2) + eps) * w, plain weight), leaves all three
 // in place and stores key and value at the token's position in the sequence's pages.
 // attn_bias: any number of new tokens per sequence after any number of cached ones; all keys are
 // read from the pages, so the step's own must be stored first.  Grid (query tiles of 32, heads,
 // sequences), 128 threads: thread t works on query row t / 4; its 4 threads split the tile's 32
 // keys (scores) and the value's elements (output) between them.
 // attn_bias_decode: one query per sequence; a block takes one head and one of `splits` ranges of
-// keys, a warp a key at a time with the lanes over the elements; ranges are merged by a second
-// kernel when there are several.
+// keys, a warp 32 keys at a time (a lane a key for the scores, then the lanes the value's
+// elements); ranges are merged by a second kernel when there are several.
 #include "common.cuh"
 
 #include <type_traits>
@@ -70,8 +70,8 @@ __global__ void attn_bias_prepare_kernel(T* __restrict__ qkv, long long ld, cons
     for (int i = lane; i < n; i += 32) {
         float x = to_f32(row[col0 + i]) + (bias ? bias[col0 + i] : 0.f);
         if (w) x = x * inv * w[i];
-        if (is_q) row[col0 + i] = from_f32<T>(x);
-        else dst[i] = from_f32<T>(x);
+        row[col0 + i] = from_f32<T>(x);              // in place too: a kernel that reads the step's own keys and values finds them ready
+        if (!is_q) dst[i] = from_f32<T>(x);
     }
 }
 
@@ -195,7 +195,27 @@ attn_bias_kernel(const T* __restrict__ q, long long q_stride, T* __restrict__ ou
 
 constexpr int DEC_WARPS = 4, DEC_MAXE = 8;      // up to 256 elements per head, lane + 32 e
 
-// part_o [n_seq, heads, splits, vdim], part_ml [n_seq, heads, splits, 2] when splits > 1
+// a key row times the query (float32 in shared memory, scaled): 16-byte loads where the row allows them
+template <typename T>
+__device__ __forceinline__ float key_dot(const T* __restrict__ kp, const float* __restrict__ qs, int dim, bool vec) {
+    float s = 0.f;
+    if (vec) {
+        constexpr int PER = 16 / sizeof(T);
+        for (int d = 0; d < dim; d += PER) {
+            const uint4 raw = *reinterpret_cast<const uint4*>(kp + d);
+            const T* x = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+            for (int e = 0; e < PER; e++) s = fmaf(qs[d + e], to_f32(x[e]), s);
+        }
+    } else {
+        for (int d = 0; d < dim; d++) s = fmaf(qs[d], to_f32(kp[d]), s);
+    }
+    return s;
+}
+
+// A warp takes 32 keys at a time: a lane a key for the scores (no sums across lanes), then the lanes the value's elements
+// while the 32 weights and rows go round by shuffles.  part_o [n_seq, heads, splits, vdim], part_ml [n_seq, heads, splits, 2]
+// when splits > 1.
 template <typename T>
 __global__ void __launch_bounds__(DEC_WARPS * 32)
 attn_bias_decode_kernel(const T* __restrict__ q, long long q_stride, T* __restrict__ out, long long o_stride,
@@ -205,6 +225,7 @@ attn_bias_decode_kernel(const T* __restrict__ q, long long q_stride, T* __restri
     ti_pdl_trigger();
     __shared__ float o_sh[DEC_WARPS][DEC_MAXE * 32];
     __shared__ float ml_sh[DEC_WARPS][2];
+    __shared__ __align__(16) float q_sh[DEC_MAXE * 32];
     ti_pdl_sync();
     q = ti_dependent(q);
     const int b = blockIdx.z, h = blockIdx.y, sp = blockIdx.x;
@@ -212,41 +233,49 @@ attn_bias_decode_kernel(const T* __restrict__ q, long long q_stride, T* __restri
     const int qi = len - 1;
     const int kvh = h / (n_heads / n_kv_heads);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int per = (len + splits - 1) / splits;
-    const int lo = sp * per, hi = min(len, lo + per);
+    // ranges of whole tiles of 32 keys
+    const int tiles = (len + 31) / 32, per = (tiles + splits - 1) / splits;
+    const int t_lo = sp * per, t_hi = min(tiles, t_lo + per);
     const float inv_cap = cap > 0.f ? 1.0f / cap : 0.f;
     const float* hb = dist_bias ? dist_bias + (size_t)h * (far + 1) : nullptr;
-    float qr[DEC_MAXE], acc[DEC_MAXE];
+    for (int d = threadIdx.x; d < dim; d += DEC_WARPS * 32) q_sh[d] = to_f32(q[(size_t)b * q_stride + (size_t)h * dim + d]) * scale;
+    __syncthreads();
+    const bool vec = (dim * sizeof(T)) % 16 == 0 && (reinterpret_cast<uintptr_t>(pg.k_pages) & 15) == 0;
+    float acc[DEC_MAXE];
 #pragma unroll
-    for (int e = 0; e < DEC_MAXE; e++) {
-        const int d = lane + 32 * e;
-        qr[e] = d < dim ? to_f32(q[(size_t)b * q_stride + (size_t)h * dim + d]) * scale : 0.f;
-        acc[e] = 0.f;
-    }
+    for (int e = 0; e < DEC_MAXE; e++) acc[e] = 0.f;
     float m_run = -INFINITY, l_run = 0.f;
-    for (int j = lo + warp; j < hi; j += DEC_WARPS) {
-        const int pidx = j / pg.page_size;
-        const int page = pidx < pg.table_width ? pg.page_table[(size_t)slot * pg.table_width + pidx] : -1;
-        if (page < 0 || page >= pg.n_pages) continue;
-        const size_t at = ((size_t)page * n_kv_heads + kvh) * pg.page_size + j % pg.page_size;
-        const T* kp = (const T*)pg.k_pages + at * dim;
-        const T* vp = (const T*)pg.v_pages + at * vdim;
-        float s = 0.f;
-#pragma unroll
-        for (int e = 0; e < DEC_MAXE; e++) {
-            const int d = lane + 32 * e;
-            if (d < dim) s = fmaf(qr[e], to_f32(kp[d]), s);
+    for (int t = t_lo + warp; t < t_hi; t += DEC_WARPS) {
+        const int j = t * 32 + lane;
+        int at = -1;                                     // the key's row among all rows of the pages
+        if (j < len) {
+            const int pidx = j / pg.page_size;
+            const int page = pidx < pg.table_width ? pg.page_table[(size_t)slot * pg.table_width + pidx] : -1;
+            if (page >= 0 && page < pg.n_pages) at = (page * n_kv_heads + kvh) * pg.page_size + j % pg.page_size;
         }
-        s = capped(warp_sum(s), cap, inv_cap);
-        if (hb) s += hb[min(qi - j, far)];
-        const float m_new = fmaxf(m_run, s);
-        const float alpha = expf(m_run - m_new), p = expf(s - m_new);
-        l_run = l_run * alpha + p;
+        float s = -INFINITY;
+        if (at >= 0) {
+            s = capped(key_dot((const T*)pg.k_pages + (size_t)at * dim, q_sh, dim, vec), cap, inv_cap);
+            if (hb) s += hb[min(qi - j, far)];
+        }
+        const float m_new = fmaxf(m_run, warp_max(s));
+        if (m_new == -INFINITY) continue;                // (the same for all lanes)
+        const float alpha = expf(m_run - m_new), p = at >= 0 ? expf(s - m_new) : 0.f;
+        l_run = l_run * alpha + warp_sum(p);
         m_run = m_new;
 #pragma unroll
-        for (int e = 0; e < DEC_MAXE; e++) {
-            const int d = lane + 32 * e;
-            if (d < vdim) acc[e] = fmaf(p, to_f32(vp[d]), acc[e] * alpha);
+        for (int e = 0; e < DEC_MAXE; e++) acc[e] *= alpha;
+#pragma unroll 4
+        for (int jj = 0; jj < 32; jj++) {
+            const float pj = __shfl_sync(0xffffffffu, p, jj);
+            const int aj = __shfl_sync(0xffffffffu, at, jj);
+            if (aj < 0) continue;
+            const T* vp = (const T*)pg.v_pages + (size_t)aj * vdim;
+#pragma unroll
+            for (int e = 0; e < DEC_MAXE; e++) {
+                const int d = lane + 32 * e;
+                if (d < vdim) acc[e] = fmaf(pj, to_f32(vp[d]), acc[e]);
+            }
         }
     }
 #pragma unroll

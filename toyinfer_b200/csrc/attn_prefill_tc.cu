@@ -50,6 +50,9 @@ struct Args {
     // PAGED form: where the positions before the step's tokens are kept
     const int* seq_start; const int* seq_slot; const int* page_table; int table_width, ring_rows, n_pages;
     const float* sink;      // per head a logit that stands in the softmax's denominator without key or value (not scaled); or null
+    // A soft cap on the scaled scores, cap * tanh(s / cap) (cap > 0), and after it a bias by distance:
+    // dist_bias[h][min(i - j, far)] is added to the score of query i and key j (float32 [heads, far + 1]; or null).
+    float cap; const float* dist_bias; int far;
 };
 
 __device__ __forceinline__ float ex2(float x) {
@@ -315,6 +318,19 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
 #pragma unroll
                 for (int e = 0; e < HALF; e++) v[e] = -INFINITY;
             }
+            if (ok && (a.cap > 0.f || a.dist_bias != nullptr)) {
+                // cap and bias work on the scaled score; what goes on from here is the result divided by the
+                // scale again, since maximum and exponent below multiply by it
+                const float inv_scale = 1.0f / a.scale, inv_cap2 = a.cap > 0.f ? 2.0f / a.cap : 0.f;
+                const float* hb = a.dist_bias ? a.dist_bias + (size_t)blockIdx.x * (a.far + 1) : nullptr;
+#pragma unroll
+                for (int e = 0; e < HALF; e++) {
+                    float x = v[e] * a.scale;
+                    if (a.cap > 0.f) x = a.cap * (1.0f - __fdividef(2.0f, __expf(x * inv_cap2) + 1.0f));      // tanh(z) = 1 - 2 / (e^2z + 1)
+                    if (hb) x += __ldg(hb + min(max(qi - (k0 + e), 0), a.far));
+                    v[e] = x * inv_scale;
+                }
+            }
             if (edge) {
 #pragma unroll
                 for (int e = 0; e < HALF; e++) {
@@ -542,6 +558,54 @@ extern "C" int ti_attn_prefill_tc_sink(const void* q, const void* k, const void*
     a.out = out; a.o_stride = o_stride; a.sink = sink;
     return head_dim == 64 ? launch<64, false>(qm, km, vm, km, vm, a, n_seq, max_new, stream)
                           : launch<128, false>(qm, km, vm, km, vm, a, n_seq, max_new, stream);
+}
+
+// The same with a soft cap on the scaled scores (cap > 0) and a bias by distance after it (dist_bias: float32
+// [n_heads, far + 1] or null; every distance from `far` on takes the last entry).
+extern "C" int ti_attn_prefill_tc_bias(const void* q, const void* k, const void* v, void* out,
+                                       long long q_stride, long long k_stride, long long v_stride, long long o_stride,
+                                       const int* cu_new, int n_seq, int max_new, int n_tokens, int n_heads, int n_kv_heads,
+                                       int head_dim, float scale, float cap, const float* dist_bias, int far, cudaStream_t stream) {
+    if (n_seq == 0 || max_new == 0) return 0;
+    TI_REQUIRE(scale > 0.f && (!dist_bias || far >= 0), "attention_prefill: a cap or a distance table needs a positive scale");
+    CUtensorMap qm, km, vm;
+    if (int rc = check_common("attention_prefill", q, k, v, out, q_stride, k_stride, v_stride, o_stride, n_seq, n_tokens,
+                              n_heads, n_kv_heads, head_dim, &qm, &km, &vm)) return rc;
+    Args a = {};
+    a.cu_new = cu_new; a.n_heads = n_heads; a.n_kv_heads = n_kv_heads; a.scale = scale; a.window = 0;
+    a.out = out; a.o_stride = o_stride; a.cap = cap; a.dist_bias = dist_bias; a.far = far;
+    return head_dim == 64 ? launch<64, false>(qm, km, vm, km, vm, a, n_seq, max_new, stream)
+                          : launch<128, false>(qm, km, vm, km, vm, a, n_seq, max_new, stream);
+}
+
+// The same for new tokens after `seq_start[b]` positions that the cache holds (pages of 64
+// positions, bfloat16); arguments as ti_attn_chunk_mma.  cap, dist_bias, far: as above (0, null, 0: none).
+extern "C" int ti_attn_chunk_tc_bias(const void* q, const void* k, const void* v, void* out,
+                                     long long q_stride, long long k_stride, long long v_stride, long long o_stride,
+                                     const int* cu_new, const int* seq_start, const int* seq_slot, int n_seq, int max_new,
+                                     int n_tokens, int n_heads, int n_kv_heads, int head_dim, float scale,
+                                     const void* k_pages, const void* v_pages, const int* page_table, int table_width,
+                                     int page_size, int n_pages, float cap, const float* dist_bias, int far, cudaStream_t stream) {
+    if (n_seq == 0 || max_new == 0) return 0;
+    TI_REQUIRE(k_pages && v_pages && page_table && seq_start && seq_slot && table_width > 0 && n_pages > 0,
+               "attention_chunk: incomplete cache description");
+    TI_REQUIRE(page_size == BKV, "attention_chunk (tcgen05): pages of %d positions, this kernel works on %d", page_size, BKV);
+    TI_REQUIRE(((reinterpret_cast<uintptr_t>(k_pages) | reinterpret_cast<uintptr_t>(v_pages)) & 15) == 0,
+               "attention_chunk (tcgen05): cache pages must be 16-byte aligned");
+    TI_REQUIRE(scale > 0.f && (!dist_bias || far >= 0), "attention_chunk: a cap or a distance table needs a positive scale");
+    CUtensorMap qm, km, vm, kpm, vpm;
+    if (int rc = check_common("attention_chunk", q, k, v, out, q_stride, k_stride, v_stride, o_stride, n_seq, n_tokens,
+                              n_heads, n_kv_heads, head_dim, &qm, &km, &vm)) return rc;
+    const long long rows = (long long)n_pages * n_kv_heads * BKV;
+    if (int rc = view_map(k_pages, rows, head_dim, head_dim, BKV, &kpm)) return rc;
+    if (int rc = view_map(v_pages, rows, head_dim, head_dim, BKV, &vpm)) return rc;
+    Args a = {};
+    a.cu_new = cu_new; a.n_heads = n_heads; a.n_kv_heads = n_kv_heads; a.scale = scale; a.window = 0;
+    a.out = out; a.o_stride = o_stride;
+    a.seq_start = seq_start; a.seq_slot = seq_slot; a.page_table = page_table; a.table_width = table_width;
+    a.ring_rows = 0; a.n_pages = n_pages; a.cap = cap; a.dist_bias = dist_bias; a.far = far;
+    return head_dim == 64 ? launch<64, true>(qm, km, vm, kpm, vpm, a, n_seq, max_new, stream)
+                          : launch<128, true>(qm, km, vm, kpm, vpm, a, n_seq, max_new, stream);
 }
 
 // The same for new tokens after `seq_start[b]` positions that the cache holds (pages of 64

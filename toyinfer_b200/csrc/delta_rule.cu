@@ -12,9 +12,9 @@
 //
 // delta_rule_scan: a sequence's new tokens are scanned in order from the state in its slot, which
 // is updated in place: whole prompts, single tokens and anything between are one kernel.  Grid
-// (heads * column groups, sequences): a thread owns one column of S (dim registers) and needs no
-// other thread's work; q, k and g of a run of tokens are staged in shared memory, where a warp
-// per token makes them ready.
+// (heads * column groups of 32, sequences): four neighbouring lanes share one column of S (dim / 4
+// registers each) and add up their parts of the two sums over the column by shuffles; q, k and g of a
+// run of tokens are staged in shared memory, where a warp per token makes them ready.
 //
 // head_gated_rmsnorm: y = o / rms(o) * w * sigmoid(gate) per token and head over vdim, w [vdim]
 // shared by the heads.
@@ -28,36 +28,45 @@ constexpr int DR_TOK = 16;       // tokens staged at a time
 
 __device__ __forceinline__ float softplus_f(float z) { return z > 20.f ? z : log1pf(expf(z)); }
 
+constexpr int DR_SPLIT = 4, DR_COLS = 32;       // a column of S is shared by 4 lanes (rows i = r, r + 4, ...); a block holds 32 columns
+
 template <typename T, int MAXD>
-__global__ void delta_rule_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v,
-                                       long long q_stride, long long k_stride, long long v_stride,
-                                       const float* __restrict__ decay_logit, const float* __restrict__ dt_bias,
-                                       const float* __restrict__ rate, const T* __restrict__ beta_logit, long long beta_stride,
-                                       float* __restrict__ o, float* __restrict__ state, long long slot_stride,
-                                       const int* __restrict__ cu_new, const int* __restrict__ seq_slot,
-                                       int n_heads, int qk_heads, int dim, int vdim, int groups) {
+__global__ void __launch_bounds__(DR_SPLIT * DR_COLS)
+delta_rule_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v,
+                       long long q_stride, long long k_stride, long long v_stride,
+                       const float* __restrict__ decay_logit, const float* __restrict__ dt_bias,
+                       const float* __restrict__ rate, const T* __restrict__ beta_logit, long long beta_stride,
+                       float* __restrict__ o, float* __restrict__ state, long long slot_stride,
+                       const int* __restrict__ cu_new, const int* __restrict__ seq_slot,
+                       int n_heads, int qk_heads, int dim, int vdim, int groups) {
     ti_pdl_trigger();
-    extern __shared__ float sm[];        // q, k, g: [DR_TOK][dim] each; beta: [DR_TOK]
+    extern __shared__ float sm[];        // q, k, g: [DR_TOK][dim] each; beta: [DR_TOK]; v: [DR_TOK][DR_COLS]
     ti_pdl_sync();
     q = ti_dependent(q); k = ti_dependent(k); v = ti_dependent(v);
     decay_logit = ti_dependent(decay_logit); beta_logit = ti_dependent(beta_logit);
+    constexpr int R = MAXD / DR_SPLIT;
     float* qs = sm;
     float* ks = qs + DR_TOK * dim;
     float* gs = ks + DR_TOK * dim;
     float* bs = gs + DR_TOK * dim;
+    float* vs = bs + DR_TOK;
     const int h = blockIdx.x / groups, g = blockIdx.x - h * groups;
     const int b = blockIdx.y;
     const int tok0 = cu_new[b], n = cu_new[b + 1] - tok0;
     if (n <= 0) return;
     const int hq = h / (n_heads / qk_heads);
-    const int col = g * blockDim.x + threadIdx.x;
+    const int r = threadIdx.x & (DR_SPLIT - 1);
+    const int col = g * DR_COLS + (threadIdx.x >> 2);
     const bool live = col < vdim;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
     const float rt = rate[h], q_scale = rsqrtf((float)dim);
-    float S[MAXD];
+    float S[R];
     float* srow = state + (size_t)seq_slot[b] * slot_stride + (size_t)h * dim * vdim;
 #pragma unroll
-    for (int i = 0; i < MAXD; i++) S[i] = (live && i < dim) ? srow[(size_t)i * vdim + col] : 0.f;
+    for (int ii = 0; ii < R; ii++) {
+        const int i = r + DR_SPLIT * ii;
+        S[ii] = (live && i < dim) ? srow[(size_t)i * vdim + col] : 0.f;
+    }
     for (int t0 = 0; t0 < n; t0 += DR_TOK) {
         const int nt = min(DR_TOK, n - t0);
         __syncthreads();
@@ -83,39 +92,50 @@ __global__ void delta_rule_scan_kernel(const T* __restrict__ q, const T* __restr
             }
             if (lane == 0) bs[tt] = 1.0f / (1.0f + expf(-to_f32(beta_logit[tok * beta_stride + h])));
         }
+        // the run's values too, all loads on their way at once: the recurrence below would wait for each in turn
+        for (int idx = threadIdx.x; idx < nt * DR_COLS; idx += blockDim.x) {
+            const int tt = idx / DR_COLS, c = g * DR_COLS + (idx - tt * DR_COLS);
+            vs[idx] = c < vdim ? to_f32(v[(size_t)(tok0 + t0 + tt) * v_stride + (size_t)h * vdim + c]) : 0.f;
+        }
         __syncthreads();
-        if (live) {
-            for (int tt = 0; tt < nt; tt++) {
-                const size_t tok = (size_t)(tok0 + t0 + tt);
-                const float vv = to_f32(v[tok * v_stride + (size_t)h * vdim + col]);
-                const float* kr = ks + tt * dim;
-                const float* qr = qs + tt * dim;
-                const float* gr = gs + tt * dim;
-                float dot = 0.f;
+        for (int tt = 0; tt < nt; tt++) {            // (all lanes take part in the sums over a column's four lanes)
+            const size_t tok = (size_t)(tok0 + t0 + tt);
+            const float vv = vs[tt * DR_COLS + (threadIdx.x >> 2)];
+            const float* kr = ks + tt * dim;
+            const float* qr = qs + tt * dim;
+            const float* gr = gs + tt * dim;
+            float dot = 0.f;
 #pragma unroll
-                for (int i = 0; i < MAXD; i++) {
-                    if (i < dim) {
-                        S[i] *= gr[i];
-                        dot = fmaf(S[i], kr[i], dot);
-                    }
+            for (int ii = 0; ii < R; ii++) {
+                const int i = r + DR_SPLIT * ii;
+                if (i < dim) {
+                    S[ii] *= gr[i];
+                    dot = fmaf(S[ii], kr[i], dot);
                 }
-                const float e = bs[tt] * (vv - dot);
-                float acc = 0.f;
-#pragma unroll
-                for (int i = 0; i < MAXD; i++) {
-                    if (i < dim) {
-                        S[i] = fmaf(kr[i], e, S[i]);
-                        acc = fmaf(S[i], qr[i], acc);
-                    }
-                }
-                o[tok * ((size_t)n_heads * vdim) + (size_t)h * vdim + col] = acc;
             }
+            dot += __shfl_xor_sync(0xffffffffu, dot, 1);
+            dot += __shfl_xor_sync(0xffffffffu, dot, 2);
+            const float e = bs[tt] * (vv - dot);
+            float acc = 0.f;
+#pragma unroll
+            for (int ii = 0; ii < R; ii++) {
+                const int i = r + DR_SPLIT * ii;
+                if (i < dim) {
+                    S[ii] = fmaf(kr[i], e, S[ii]);
+                    acc = fmaf(S[ii], qr[i], acc);
+                }
+            }
+            acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+            acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+            if (live && r == 0) o[tok * ((size_t)n_heads * vdim) + (size_t)h * vdim + col] = acc;
         }
     }
     if (live) {
 #pragma unroll
-        for (int i = 0; i < MAXD; i++)
-            if (i < dim) srow[(size_t)i * vdim + col] = S[i];
+        for (int ii = 0; ii < R; ii++) {
+            const int i = r + DR_SPLIT * ii;
+            if (i < dim) srow[(size_t)i * vdim + col] = S[ii];
+        }
     }
 }
 
@@ -164,8 +184,8 @@ extern "C" int ti_delta_rule_scan(const void* q, const void* k, const void* v, l
     TI_REQUIRE(n_seq > 0 && n_seq <= 65535 && n_heads > 0 && qk_heads > 0 && n_heads % qk_heads == 0 && dim > 0 && vdim > 0,
                "delta_rule_scan: bad sizes");
     TI_REQUIRE(dim <= 128, "delta_rule: heads of %d query/key elements are not supported (up to 128)", dim);
-    const int threads = vdim <= 32 ? 32 : vdim <= 64 ? 64 : 128, groups = (vdim + threads - 1) / threads;
-    const size_t smem = (size_t)(3 * DR_TOK * dim + DR_TOK) * sizeof(float);
+    const int threads = DR_SPLIT * DR_COLS, groups = (vdim + DR_COLS - 1) / DR_COLS;
+    const size_t smem = (size_t)(3 * DR_TOK * dim + DR_TOK + DR_TOK * DR_COLS) * sizeof(float);
     return ti_dispatch_dtype(dtype, [&](auto t) -> int {
         using T = decltype(t);
         return dispatch_dim(dim, [&](auto md) -> int {

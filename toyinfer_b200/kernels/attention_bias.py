@@ -41,15 +41,21 @@ def prepare(qkv: torch.Tensor, bias: Optional[torch.Tensor], q_w: Optional[torch
 
 
 def decode_splits(n_seq: int, n_heads: int, plan_len: int, sms: int) -> int:
-    """Ranges that a single query's keys are cut into, so that the step has about two blocks per SM but no range
+    """Ranges that a single query's keys are cut into, so that the step has about four blocks per SM but no range
     shorter than 256 keys: depends only on the batch's padded size and the length the step was planned for."""
-    want = max(1, (2 * sms) // max(1, n_seq * n_heads))
+    want = max(1, (4 * sms) // max(1, n_seq * n_heads))
     return max(1, min(want, (plan_len + 255) // 256, 64))
 
 
-def attend(q: torch.Tensor, vdim: int, mem, scale: float, cap: float, dist_bias: Optional[torch.Tensor], batch) -> torch.Tensor:
+tensor_cores = True          # tests clear this to run prompts and pieces on the CUDA-core kernel whatever their sizes
+
+
+def attend(q: torch.Tensor, vdim: int, mem, scale: float, cap: float, dist_bias: Optional[torch.Tensor], batch,
+           k: Optional[torch.Tensor] = None, v: Optional[torch.Tensor] = None) -> torch.Tensor:
     """q [M, heads, dim] (normed) over the keys and values that ``mem`` holds, the step's own included -> [M, heads * vdim].
-    dist_bias: float32 [heads, far + 1], the bias of every distance up to ``far`` (all further ones share the last)."""
+    dist_bias: float32 [heads, far + 1], the bias of every distance up to ``far`` (all further ones share the last).
+    k, v: the step's own keys [M, kv_heads, dim] and values [M, kv_heads, vdim] as they were stored, for the
+    tensor-core kernel (bfloat16, heads of 64 or 128 elements for keys and values alike)."""
     _need_cuda(q, dist_bias, what="attention_bias")
     M, H, dim = q.shape
     if q.stride(2) != 1 or q.stride(1) != dim:
@@ -72,6 +78,21 @@ def attend(q: torch.Tensor, vdim: int, mem, scale: float, cap: float, dist_bias:
               _ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(batch.seq_len), _ptr(batch.seq_slot), M, *pages, _ptr(dist_bias),
               far, H, mem.n_kv_heads, dim, vdim, float(scale), float(cap), splits, _ptr(part_o), _ptr(part_ml), code, _stream(),
               launches=2 if splits > 1 else 1)
+        return out
+    G = mem.n_kv_heads
+    if tensor_cores and q.dtype == torch.bfloat16 and dim == vdim and dim in (64, 128) and k is not None and mem.page_size == 64 \
+            and all(t.stride(0) % 8 == 0 and t.data_ptr() % 16 == 0 for t in (q, k, v, out)) and scale > 0:
+        # whole prompts and pieces on tcgen05: the kernel of the other attention mixers, told of cap and table
+        # (csrc/attn_prefill_tc.cu); it reads the step's own keys and values beside the pages
+        if batch.mode == "start":
+            _call(_fn("ti_attn_prefill_tc_bias", [P, P, P, P, L, L, L, L, P, I, I, I, I, I, I, F, F, P, I, P]),
+                  _ptr(q), _ptr(k), _ptr(v), _ptr(out), q.stride(0), k.stride(0), v.stride(0), out.stride(0), _ptr(batch.cu_new),
+                  batch.n_seq, batch.max_new, M, H, G, dim, float(scale), float(cap), _ptr(dist_bias), far, _stream())
+        else:
+            _call(_fn("ti_attn_chunk_tc_bias", [P, P, P, P, L, L, L, L, P, P, P, I, I, I, I, I, I, F, P, P, P, I, I, I, F, P, I, P]),
+                  _ptr(q), _ptr(k), _ptr(v), _ptr(out), q.stride(0), k.stride(0), v.stride(0), out.stride(0), _ptr(batch.cu_new),
+                  _ptr(batch.seq_start), _ptr(batch.seq_slot), batch.n_seq, batch.max_new, M, H, G, dim, float(scale), *pages,
+                  float(cap), _ptr(dist_bias), far, _stream())
         return out
     _call(_fn("ti_attn_bias", [P, L, P, L, P, P, P, I, I, P, P, P, I, I, I, P, I, I, I, I, I, F, F, I, P]),
           _ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(batch.cu_new), _ptr(batch.seq_start), _ptr(batch.seq_slot),

@@ -53,6 +53,9 @@ def short_conv(x: torch.Tensor, taps: torch.Tensor, state: torch.Tensor, state_o
     return out
 
 
+RGLRU_CHUNKED_FROM = 256        # new tokens of one sequence from which a step runs the chunked form (three launches)
+
+
 def rglru_scan(gates: torch.Tensor, u: torch.Tensor, z: torch.Tensor, gate_bias_r: torch.Tensor, gate_bias_i: torch.Tensor,
                z_bias: Optional[torch.Tensor], rate: torch.Tensor, block: int, state: torch.Tensor, state_offset: int, batch) -> torch.Tensor:
     """gates float32 [M, 2 C] (per gate block of ``block`` channels: its recurrence-gate logits, then its input-gate
@@ -67,6 +70,14 @@ def rglru_scan(gates: torch.Tensor, u: torch.Tensor, z: torch.Tensor, gate_bias_
         _vec(t, C, f"rglru_scan: the {what}")
     base, stride = _state_part(state, state_offset, C, "rglru_scan")
     out = torch.zeros((M, C), dtype=u.dtype, device=u.device)
+    if batch.max_new >= RGLRU_CHUNKED_FROM:
+        chunks = (batch.max_new + 127) // 128
+        scratch = torch.empty((batch.n_seq, chunks, 2, C), dtype=torch.float32, device=u.device)
+        _call(_fn("ti_rglru_scan_chunked", [P, P, L, P, L, P, P, P, P, P, L, P, P, P, P, I, I, I, I, I, P]),
+              _ptr(gates), _ptr(u), u.stride(0), _ptr(z), z.stride(0), _ptr(gate_bias_r), _ptr(gate_bias_i), _ptr(z_bias), _ptr(rate),
+              base, stride, _ptr(out), _ptr(scratch), _ptr(batch.cu_new), _ptr(batch.seq_slot), batch.n_seq, batch.max_new, C, int(block),
+              _code(u, "rglru_scan"), _stream(), launches=3)
+        return out
     _call(_fn("ti_rglru_scan", [P, P, L, P, L, P, P, P, P, P, L, P, P, P, I, I, I, I, P]),
           _ptr(gates), _ptr(u), u.stride(0), _ptr(z), z.stride(0), _ptr(gate_bias_r), _ptr(gate_bias_i), _ptr(z_bias), _ptr(rate),
           base, stride, _ptr(out), _ptr(batch.cu_new), _ptr(batch.seq_slot), batch.n_seq, C, int(block), _code(u, "rglru_scan"), _stream())
@@ -112,4 +123,28 @@ def head_gated_rmsnorm(o: torch.Tensor, gate: torch.Tensor, w: torch.Tensor, n_h
     out = torch.empty((M, N), dtype=gate.dtype, device=o.device)
     _call(_fn("ti_head_gated_rmsnorm", [P, P, L, P, P, I, I, I, F, I, P]), _ptr(o), _ptr(gate), gate.stride(0), _ptr(w), _ptr(out),
           M, int(n_heads), N // n_heads, float(eps), _code(gate, "head_gated_rmsnorm"), _stream())
+    return out
+
+
+BLOCK_DIAG_MAX_TOKENS = 64      # up to this many tokens all blocks' products are one launch; beyond, a product per block
+
+
+def block_diag_linear(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """x [M, blocks * K] times a block-diagonal matrix given as w [blocks, N, K] -> float32 [M, blocks * N]: block b of the
+    result is x's b-th K columns times w[b] transposed.  Few tokens: one kernel that reads every weight once (csrc/rglru.cu);
+    many: the library's product, block by block."""
+    _need_cuda(x, w, what="block_diag_linear")
+    nb, N, Kb = w.shape
+    M = x.shape[0]
+    if x.dim() != 2 or x.shape[1] != nb * Kb or x.stride(1) != 1 or w.dtype != x.dtype or not w.is_contiguous():
+        raise KernelError("block_diag_linear: the rows do not fit the blocks")
+    out = torch.empty((M, nb * N), dtype=torch.float32, device=x.device)
+    if M <= BLOCK_DIAG_MAX_TOKENS:
+        _call(_fn("ti_block_diag_linear", [P, L, P, P, L, I, I, I, I, I, P]), _ptr(x), x.stride(0), _ptr(w), _ptr(out), out.stride(0), M,
+              nb, N, Kb, _code(x, "block_diag_linear"), _stream())
+        return out
+    from . import gemm
+    for b in range(nb):
+        xb, wb, ob = x[:, b * Kb:(b + 1) * Kb], w[b], out[:, b * N:(b + 1) * N]
+        gemm.run(xb, wb, ob, M, N, Kb, xb.stride(0), wb.stride(0))
     return out

@@ -115,7 +115,9 @@ class BiasedAttention(Mixer):
         M = qkv.shape[0]
         with ranged(batch, "mixer.attention"):
             KA.prepare(qkv, self.b_qkv, self.q_w, self.k_w, self.eps, H, self.n_kv, d, self.vdim, mem, batch)
-            a = KA.attend(qkv[:, :H * d].view(M, H, d), self.vdim, mem, self.scale, self.softcap, self.dist_bias, batch)
+            G, vd = self.n_kv, self.vdim
+            a = KA.attend(qkv[:, :H * d].view(M, H, d), vd, mem, self.scale, self.softcap, self.dist_bias, batch,
+                          k=qkv[:, H * d:(H + G) * d].view(M, G, d), v=qkv[:, (H + G) * d:].view(M, G, vd))
         with ranged(batch, "mixer.out"):
             return K.linear_bias(a, self.w_o, self.b_o)
 

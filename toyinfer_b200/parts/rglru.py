@@ -18,7 +18,7 @@ from typing import Dict, Optional
 import torch
 
 from .. import kernels as K
-from ..kernels import gemm, recurrent as KR
+from ..kernels import recurrent as KR
 from ..tracing import ranged
 from .base import BuildContext, Mixer, ParamSpec, StateRequest, register_part
 
@@ -79,12 +79,8 @@ class RGLRUBlock(Mixer):
         C, bs = self.width, self.width // self.blocks
         with ranged(batch, "mixer.qkv"):
             xy = K.linear(x, self.w_in)
-            M = xy.shape[0]
             u = KR.short_conv(xy[:, :C], self.conv_w, mem.state, self.state_conv, batch, in_bias=self.b_x, out_bias=self.conv_b)
-            gates = torch.empty((M, 2 * C), dtype=torch.float32, device=u.device)
-            for b in range(self.blocks):
-                ub, wb, ob = u[:, b * bs:(b + 1) * bs], self.w_gates[b], gates[:, 2 * b * bs:2 * (b + 1) * bs]
-                gemm.run(ub, wb, ob, M, 2 * bs, bs, ub.stride(0), wb.stride(0))
+            gates = KR.block_diag_linear(u, self.w_gates)
         with ranged(batch, "mixer.attention"):
             s = KR.rglru_scan(gates, u, xy[:, C:], self.b_r, self.b_i, self.b_y, self.rate, bs, mem.state, self.state_s, batch)
         with ranged(batch, "mixer.out"):
