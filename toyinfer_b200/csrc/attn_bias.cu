@@ -16,9 +16,9 @@
 // read from the pages, so the step's own must be stored first.  Grid (query tiles of 32, heads,
 // sequences), 128 threads: thread t works on query row t / 4; its 4 threads split the tile's 32
 // keys (scores) and the value's elements (output) between them.
-// attn_bias_decode: one query per sequence; a block takes one head and one of `splits` ranges of
-// keys, a warp 32 keys at a time (a lane a key for the scores, then the lanes the value's
-// elements); ranges are merged by a second kernel when there are several.
+// attn_bias_decode: one query per sequence; a block takes up to four query heads of one kv head and
+// one of `splits` ranges of keys, a warp 32 keys at a time (a lane a key for the scores, then the
+// lanes the value's elements); ranges are merged by a second kernel when there are several.
 #include "common.cuh"
 
 #include <type_traits>
@@ -195,56 +195,61 @@ attn_bias_kernel(const T* __restrict__ q, long long q_stride, T* __restrict__ ou
 
 constexpr int DEC_WARPS = 4, DEC_MAXE = 8;      // up to 256 elements per head, lane + 32 e
 
-// a key row times the query (float32 in shared memory, scaled): 16-byte loads where the row allows them
-template <typename T>
-__device__ __forceinline__ float key_dot(const T* __restrict__ kp, const float* __restrict__ qs, int dim, bool vec) {
-    float s = 0.f;
-    if (vec) {
-        constexpr int PER = 16 / sizeof(T);
-        for (int d = 0; d < dim; d += PER) {
-            const uint4 raw = *reinterpret_cast<const uint4*>(kp + d);
-            const T* x = reinterpret_cast<const T*>(&raw);
+// `n` consecutive elements of a row as floats, by one load where size and address allow it
+template <typename T, int N>
+__device__ __forceinline__ void load_run(const T* __restrict__ p, float (&x)[N], bool vec) {
+    constexpr int BYTES = N * (int)sizeof(T);
+    if (vec && (BYTES == 16 || BYTES == 8 || BYTES == 4)) {
+        T raw[N];
+        if constexpr (BYTES == 16) *reinterpret_cast<uint4*>(raw) = *reinterpret_cast<const uint4*>(p);
+        else if constexpr (BYTES == 8) *reinterpret_cast<uint2*>(raw) = *reinterpret_cast<const uint2*>(p);
+        else if constexpr (BYTES == 4) *reinterpret_cast<uint32_t*>(raw) = *reinterpret_cast<const uint32_t*>(p);
 #pragma unroll
-            for (int e = 0; e < PER; e++) s = fmaf(qs[d + e], to_f32(x[e]), s);
-        }
+        for (int e = 0; e < N; e++) x[e] = to_f32(raw[e]);
     } else {
-        for (int d = 0; d < dim; d++) s = fmaf(qs[d], to_f32(kp[d]), s);
+#pragma unroll
+        for (int e = 0; e < N; e++) x[e] = to_f32(p[e]);
     }
-    return s;
 }
 
-// A warp takes 32 keys at a time: a lane a key for the scores (no sums across lanes), then the lanes the value's elements
-// while the 32 weights and rows go round by shuffles.  part_o [n_seq, heads, splits, vdim], part_ml [n_seq, heads, splits, 2]
-// when splits > 1.
-template <typename T>
+// A block takes GH query heads that share a kv head, and one range of keys; a warp 32 keys at a time: a lane a key for
+// the scores of all GH heads (the key's row is read once, 16 bytes at a time where it allows; no sums across lanes), then
+// the lanes VPL consecutive elements of the value each, while the 32 weights and rows go round by shuffles.
+// part_o [n_seq, heads, splits, vdim], part_ml [n_seq, heads, splits, 2] when splits > 1.
+template <typename T, int GH, int VPL>
 __global__ void __launch_bounds__(DEC_WARPS * 32)
 attn_bias_decode_kernel(const T* __restrict__ q, long long q_stride, T* __restrict__ out, long long o_stride,
                         const int* __restrict__ seq_len, const int* __restrict__ seq_slot, Pages pg,
                         const float* __restrict__ dist_bias, int far, int n_heads, int n_kv_heads, int dim, int vdim,
                         float scale, float cap, int splits, float* __restrict__ part_o, float* __restrict__ part_ml) {
     ti_pdl_trigger();
-    __shared__ float o_sh[DEC_WARPS][DEC_MAXE * 32];
-    __shared__ float ml_sh[DEC_WARPS][2];
-    __shared__ __align__(16) float q_sh[DEC_MAXE * 32];
+    extern __shared__ __align__(16) float dsm[];         // q: [GH][dim]; o: [DEC_WARPS][GH][32 * VPL]; m, l: [DEC_WARPS][GH][2]
+    float* q_sh = dsm;
+    float* o_sh = q_sh + GH * dim;
+    float* ml_sh = o_sh + DEC_WARPS * GH * 32 * VPL;
     ti_pdl_sync();
     q = ti_dependent(q);
-    const int b = blockIdx.z, h = blockIdx.y, sp = blockIdx.x;
+    const int b = blockIdx.z, h0 = blockIdx.y * GH, sp = blockIdx.x;
     const int len = seq_len[b], slot = seq_slot[b];
     const int qi = len - 1;
-    const int kvh = h / (n_heads / n_kv_heads);
+    const int kvh = h0 / (n_heads / n_kv_heads);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    // ranges of whole tiles of 32 keys
-    const int tiles = (len + 31) / 32, per = (tiles + splits - 1) / splits;
+    const int tiles = (len + 31) / 32, per = (tiles + splits - 1) / splits;          // ranges of whole tiles of 32 keys
     const int t_lo = sp * per, t_hi = min(tiles, t_lo + per);
     const float inv_cap = cap > 0.f ? 1.0f / cap : 0.f;
-    const float* hb = dist_bias ? dist_bias + (size_t)h * (far + 1) : nullptr;
-    for (int d = threadIdx.x; d < dim; d += DEC_WARPS * 32) q_sh[d] = to_f32(q[(size_t)b * q_stride + (size_t)h * dim + d]) * scale;
+    for (int i = threadIdx.x; i < GH * dim; i += DEC_WARPS * 32)
+        q_sh[i] = to_f32(q[(size_t)b * q_stride + (size_t)h0 * dim + i]) * scale;
     __syncthreads();
-    const bool vec = (dim * sizeof(T)) % 16 == 0 && (reinterpret_cast<uintptr_t>(pg.k_pages) & 15) == 0;
-    float acc[DEC_MAXE];
+    const bool kvec = (dim * sizeof(T)) % 16 == 0 && (reinterpret_cast<uintptr_t>(pg.k_pages) & 15) == 0;
+    const bool vvec = vdim % VPL == 0 && (reinterpret_cast<uintptr_t>(pg.v_pages) & 15) == 0;
+    constexpr int KPER = 16 / sizeof(T);
+    float acc[GH][VPL], m_run[GH], l_run[GH];
 #pragma unroll
-    for (int e = 0; e < DEC_MAXE; e++) acc[e] = 0.f;
-    float m_run = -INFINITY, l_run = 0.f;
+    for (int g = 0; g < GH; g++) {
+        m_run[g] = -INFINITY; l_run[g] = 0.f;
+#pragma unroll
+        for (int e = 0; e < VPL; e++) acc[g][e] = 0.f;
+    }
     for (int t = t_lo + warp; t < t_hi; t += DEC_WARPS) {
         const int j = t * 32 + lane;
         int at = -1;                                     // the key's row among all rows of the pages
@@ -253,54 +258,100 @@ attn_bias_decode_kernel(const T* __restrict__ q, long long q_stride, T* __restri
             const int page = pidx < pg.table_width ? pg.page_table[(size_t)slot * pg.table_width + pidx] : -1;
             if (page >= 0 && page < pg.n_pages) at = (page * n_kv_heads + kvh) * pg.page_size + j % pg.page_size;
         }
-        float s = -INFINITY;
-        if (at >= 0) {
-            s = capped(key_dot((const T*)pg.k_pages + (size_t)at * dim, q_sh, dim, vec), cap, inv_cap);
-            if (hb) s += hb[min(qi - j, far)];
-        }
-        const float m_new = fmaxf(m_run, warp_max(s));
-        if (m_new == -INFINITY) continue;                // (the same for all lanes)
-        const float alpha = expf(m_run - m_new), p = at >= 0 ? expf(s - m_new) : 0.f;
-        l_run = l_run * alpha + warp_sum(p);
-        m_run = m_new;
+        float s[GH];
 #pragma unroll
-        for (int e = 0; e < DEC_MAXE; e++) acc[e] *= alpha;
+        for (int g = 0; g < GH; g++) s[g] = 0.f;
+        if (at >= 0) {
+            const T* kp = (const T*)pg.k_pages + (size_t)at * dim;
+            if (kvec) {
+                for (int d = 0; d < dim; d += KPER) {
+                    float x[KPER];
+                    load_run<T, KPER>(kp + d, x, true);
+#pragma unroll
+                    for (int g = 0; g < GH; g++)
+#pragma unroll
+                        for (int e = 0; e < KPER; e++) s[g] = fmaf(q_sh[g * dim + d + e], x[e], s[g]);
+                }
+            } else {
+                for (int d = 0; d < dim; d++) {
+                    const float x = to_f32(kp[d]);
+#pragma unroll
+                    for (int g = 0; g < GH; g++) s[g] = fmaf(q_sh[g * dim + d], x, s[g]);
+                }
+            }
+        }
+        float p[GH];
+        bool any = false;
+#pragma unroll
+        for (int g = 0; g < GH; g++) {
+            float x = -INFINITY;
+            if (at >= 0) {
+                x = capped(s[g], cap, inv_cap);
+                if (dist_bias) x += dist_bias[(size_t)(h0 + g) * (far + 1) + min(qi - j, far)];
+            }
+            const float m_new = fmaxf(m_run[g], warp_max(x));
+            p[g] = 0.f;
+            if (m_new > -INFINITY) {                     // (the same for all lanes)
+                const float alpha = expf(m_run[g] - m_new);
+                p[g] = at >= 0 ? expf(x - m_new) : 0.f;
+                l_run[g] = l_run[g] * alpha + warp_sum(p[g]);
+                m_run[g] = m_new;
+#pragma unroll
+                for (int e = 0; e < VPL; e++) acc[g][e] *= alpha;
+                any = true;
+            }
+        }
+        if (!any) continue;
 #pragma unroll 4
         for (int jj = 0; jj < 32; jj++) {
-            const float pj = __shfl_sync(0xffffffffu, p, jj);
             const int aj = __shfl_sync(0xffffffffu, at, jj);
-            if (aj < 0) continue;
-            const T* vp = (const T*)pg.v_pages + (size_t)aj * vdim;
+            float x[VPL];
+            const T* vp = (const T*)pg.v_pages + (size_t)max(aj, 0) * vdim + lane * VPL;
+            if (vvec) {
+                if (lane * VPL < vdim) load_run<T, VPL>(vp, x, true);
+            } else {
 #pragma unroll
-            for (int e = 0; e < DEC_MAXE; e++) {
-                const int d = lane + 32 * e;
-                if (d < vdim) acc[e] = fmaf(pj, to_f32(vp[d]), acc[e]);
+                for (int e = 0; e < VPL; e++) x[e] = lane * VPL + e < vdim ? to_f32(vp[e]) : 0.f;
+            }
+#pragma unroll
+            for (int g = 0; g < GH; g++) {
+                const float pj = __shfl_sync(0xffffffffu, p[g], jj);       // 0 where the lane's key does not exist
+#pragma unroll
+                for (int e = 0; e < VPL; e++)
+                    if (aj >= 0 && lane * VPL + e < vdim) acc[g][e] = fmaf(pj, x[e], acc[g][e]);
             }
         }
     }
 #pragma unroll
-    for (int e = 0; e < DEC_MAXE; e++) o_sh[warp][lane + 32 * e] = acc[e];
-    if (lane == 0) { ml_sh[warp][0] = m_run; ml_sh[warp][1] = l_run; }
+    for (int g = 0; g < GH; g++) {
+#pragma unroll
+        for (int e = 0; e < VPL; e++) o_sh[(warp * GH + g) * 32 * VPL + lane * VPL + e] = acc[g][e];
+        if (lane == 0) { ml_sh[(warp * GH + g) * 2] = m_run[g]; ml_sh[(warp * GH + g) * 2 + 1] = l_run[g]; }
+    }
     __syncthreads();
-    float m_all = -INFINITY;
+    for (int g = 0; g < GH; g++) {
+        const int h = h0 + g;
+        float m_all = -INFINITY;
 #pragma unroll
-    for (int w = 0; w < DEC_WARPS; w++) m_all = fmaxf(m_all, ml_sh[w][0]);
-    float l_all = 0.f, f[DEC_WARPS];
+        for (int w = 0; w < DEC_WARPS; w++) m_all = fmaxf(m_all, ml_sh[(w * GH + g) * 2]);
+        float l_all = 0.f, f[DEC_WARPS];
 #pragma unroll
-    for (int w = 0; w < DEC_WARPS; w++) {
-        f[w] = ml_sh[w][0] > -INFINITY ? expf(ml_sh[w][0] - m_all) : 0.f;
-        l_all += ml_sh[w][1] * f[w];
-    }
-    for (int d = threadIdx.x; d < vdim; d += DEC_WARPS * 32) {
-        float o = 0.f;
+        for (int w = 0; w < DEC_WARPS; w++) {
+            const float mw = ml_sh[(w * GH + g) * 2];
+            f[w] = mw > -INFINITY ? expf(mw - m_all) : 0.f;
+            l_all += ml_sh[(w * GH + g) * 2 + 1] * f[w];
+        }
+        for (int d = threadIdx.x; d < vdim; d += DEC_WARPS * 32) {
+            float o = 0.f;
 #pragma unroll
-        for (int w = 0; w < DEC_WARPS; w++) o = fmaf(o_sh[w][d], f[w], o);
-        if (splits == 1) out[(size_t)b * o_stride + (size_t)h * vdim + d] = from_f32<T>(l_all > 0.f ? o / l_all : 0.f);
-        else part_o[(((size_t)b * n_heads + h) * splits + sp) * vdim + d] = o;
-    }
-    if (splits > 1 && threadIdx.x == 0) {
-        float* ml = part_ml + (((size_t)b * n_heads + h) * splits + sp) * 2;
-        ml[0] = m_all; ml[1] = l_all;
+            for (int w = 0; w < DEC_WARPS; w++) o = fmaf(o_sh[(w * GH + g) * 32 * VPL + d], f[w], o);
+            if (splits == 1) out[(size_t)b * o_stride + (size_t)h * vdim + d] = from_f32<T>(l_all > 0.f ? o / l_all : 0.f);
+            else part_o[(((size_t)b * n_heads + h) * splits + sp) * vdim + d] = o;
+        }
+        if (splits > 1 && threadIdx.x == 0) {
+            float* ml = part_ml + (((size_t)b * n_heads + h) * splits + sp) * 2;
+            ml[0] = m_all; ml[1] = l_all;
+        }
     }
 }
 
@@ -403,12 +454,37 @@ extern "C" int ti_attn_bias_decode(const void* q, long long q_stride, void* out,
     TI_REQUIRE(splits == 1 || (part_o && part_ml), "attn_bias_decode: split keys need scratch");
     if (check_pages("attn_bias_decode", k_pages, v_pages, page_table, table_width, page_size, n_pages)) return 1;
     Pages pg{k_pages, v_pages, page_table, table_width, page_size, n_pages};
+    // query heads of one kv head per block: as many of 4, 2, 1 as divide the group; value elements per lane: 1, 2, 4 or 8
+    const int group = n_heads / n_kv_heads;
+    const int gh = group % 4 == 0 ? 4 : group % 2 == 0 ? 2 : 1;
+    const int vpl = vdim <= 32 ? 1 : vdim <= 64 ? 2 : vdim <= 128 ? 4 : 8;
     return ti_dispatch_dtype(dtype, [&](auto t) -> int {
         using T = decltype(t);
-        TI_CUDA(ti_launch_class<3>(attn_bias_decode_kernel<T>, dim3(splits, n_heads, n_seq), dim3(DEC_WARPS * 32), 0, stream, (const T*)q,
-                                   q_stride, (T*)out, o_stride, seq_len, seq_slot, pg, dist_bias, far, n_heads, n_kv_heads, dim, vdim,
-                                   scale, cap, splits, part_o, part_ml));
-        TI_CHECK_LAUNCH("attn_bias_decode");
+        auto go = [&](auto ghv, auto vplv) -> int {
+            constexpr int GH = decltype(ghv)::value, VPL = decltype(vplv)::value;
+            const size_t smem = ((size_t)GH * dim + (size_t)DEC_WARPS * GH * 32 * VPL + (size_t)DEC_WARPS * GH * 2) * sizeof(float);
+            static size_t configured = 0;
+            if (smem > 48 * 1024 && smem > configured) {
+                TI_CUDA(cudaFuncSetAttribute(attn_bias_decode_kernel<T, GH, VPL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+                configured = smem;
+            }
+            TI_CUDA(ti_launch_class<3>(attn_bias_decode_kernel<T, GH, VPL>, dim3(splits, n_heads / GH, n_seq), dim3(DEC_WARPS * 32), smem, stream,
+                                       (const T*)q, q_stride, (T*)out, o_stride, seq_len, seq_slot, pg, dist_bias, far, n_heads, n_kv_heads,
+                                       dim, vdim, scale, cap, splits, part_o, part_ml));
+            TI_CHECK_LAUNCH("attn_bias_decode");
+            return 0;
+        };
+        auto with_vpl = [&](auto ghv) -> int {
+            switch (vpl) {
+                case 1: return go(ghv, std::integral_constant<int, 1>());
+                case 2: return go(ghv, std::integral_constant<int, 2>());
+                case 4: return go(ghv, std::integral_constant<int, 4>());
+                default: return go(ghv, std::integral_constant<int, 8>());
+            }
+        };
+        int rc = gh == 4 ? with_vpl(std::integral_constant<int, 4>()) : gh == 2 ? with_vpl(std::integral_constant<int, 2>())
+                                                                                 : with_vpl(std::integral_constant<int, 1>());
+        if (rc) return rc;
         if (splits > 1) {
             TI_CUDA(ti_launch_class<4>(attn_bias_merge_kernel<T>, dim3(n_heads, n_seq), dim3(64), 0, stream, (const float*)part_o,
                                        (const float*)part_ml, (T*)out, o_stride, n_heads, vdim, splits));

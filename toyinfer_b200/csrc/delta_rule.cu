@@ -12,9 +12,9 @@
 //
 // delta_rule_scan: a sequence's new tokens are scanned in order from the state in its slot, which
 // is updated in place: whole prompts, single tokens and anything between are one kernel.  Grid
-// (heads * column groups of 32, sequences): four neighbouring lanes share one column of S (dim / 4
-// registers each) and add up their parts of the two sums over the column by shuffles; q, k and g of a
-// run of tokens are staged in shared memory, where a warp per token makes them ready.
+// (heads * column groups of 32, sequences): four neighbouring lanes share one column of S (a quarter
+// of its rows in registers each) and add up their parts of the two sums over the column by shuffles;
+// q, k, g and v of a run of tokens are staged in shared memory, where a warp per token makes them ready.
 //
 // head_gated_rmsnorm: y = o / rms(o) * w * sigmoid(gate) per token and head over vdim, w [vdim]
 // shared by the heads.
@@ -28,8 +28,11 @@ constexpr int DR_TOK = 16;       // tokens staged at a time
 
 __device__ __forceinline__ float softplus_f(float z) { return z > 20.f ? z : log1pf(expf(z)); }
 
-constexpr int DR_SPLIT = 4, DR_COLS = 32;       // a column of S is shared by 4 lanes (rows i = r, r + 4, ...); a block holds 32 columns
+constexpr int DR_SPLIT = 4, DR_COLS = 32;       // a column of S is shared by 4 lanes; a block holds 32 columns
 
+// Lane r of a column's four holds the rows i = 16 jj + 4 r + e (e < 4): its q, k and g come as one 16-byte read per jj
+// from shared memory, the four lanes' reads side by side.  Staged rows are MAXD long, zero past dim, so that the inner
+// loops have no bounds to check (rows of S past dim stay zero).
 template <typename T, int MAXD>
 __global__ void __launch_bounds__(DR_SPLIT * DR_COLS)
 delta_rule_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v,
@@ -40,16 +43,16 @@ delta_rule_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T
                        const int* __restrict__ cu_new, const int* __restrict__ seq_slot,
                        int n_heads, int qk_heads, int dim, int vdim, int groups) {
     ti_pdl_trigger();
-    extern __shared__ float sm[];        // q, k, g: [DR_TOK][dim] each; beta: [DR_TOK]; v: [DR_TOK][DR_COLS]
+    extern __shared__ __align__(16) float sm[];        // q, k, g: [DR_TOK][MAXD] each; v: [DR_TOK][DR_COLS]; beta: [DR_TOK]
     ti_pdl_sync();
     q = ti_dependent(q); k = ti_dependent(k); v = ti_dependent(v);
     decay_logit = ti_dependent(decay_logit); beta_logit = ti_dependent(beta_logit);
-    constexpr int R = MAXD / DR_SPLIT;
+    constexpr int J = MAXD / 16;
     float* qs = sm;
-    float* ks = qs + DR_TOK * dim;
-    float* gs = ks + DR_TOK * dim;
-    float* bs = gs + DR_TOK * dim;
-    float* vs = bs + DR_TOK;
+    float* ks = qs + DR_TOK * MAXD;
+    float* gs = ks + DR_TOK * MAXD;
+    float* vs = gs + DR_TOK * MAXD;
+    float* bs = vs + DR_TOK * DR_COLS;
     const int h = blockIdx.x / groups, g = blockIdx.x - h * groups;
     const int b = blockIdx.y;
     const int tok0 = cu_new[b], n = cu_new[b + 1] - tok0;
@@ -60,35 +63,41 @@ delta_rule_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T
     const bool live = col < vdim;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
     const float rt = rate[h], q_scale = rsqrtf((float)dim);
-    float S[R];
+    float S[J][4];
     float* srow = state + (size_t)seq_slot[b] * slot_stride + (size_t)h * dim * vdim;
 #pragma unroll
-    for (int ii = 0; ii < R; ii++) {
-        const int i = r + DR_SPLIT * ii;
-        S[ii] = (live && i < dim) ? srow[(size_t)i * vdim + col] : 0.f;
-    }
+    for (int jj = 0; jj < J; jj++)
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+            const int i = 16 * jj + 4 * r + e;
+            S[jj][e] = (live && i < dim) ? srow[(size_t)i * vdim + col] : 0.f;
+        }
     for (int t0 = 0; t0 < n; t0 += DR_TOK) {
         const int nt = min(DR_TOK, n - t0);
         __syncthreads();
         for (int tt = warp; tt < nt; tt += n_warps) {
             const size_t tok = (size_t)(tok0 + t0 + tt);
             float sq = 0.f, sk = 0.f;
-            for (int i = lane; i < dim; i += 32) {
-                const float qv = to_f32(q[tok * q_stride + (size_t)hq * dim + i]);
-                const float kv = to_f32(k[tok * k_stride + (size_t)hq * dim + i]);
-                qs[tt * dim + i] = qv;
-                ks[tt * dim + i] = kv;
+            for (int i = lane; i < MAXD; i += 32) {
+                float qv = 0.f, kv = 0.f, gv = 0.f;
+                if (i < dim) {
+                    qv = to_f32(q[tok * q_stride + (size_t)hq * dim + i]);
+                    kv = to_f32(k[tok * k_stride + (size_t)hq * dim + i]);
+                    const float l = decay_logit[tok * ((size_t)n_heads * dim) + (size_t)h * dim + i] + dt_bias[(size_t)h * dim + i];
+                    gv = expf(-rt * softplus_f(l));
+                }
+                qs[tt * MAXD + i] = qv;
+                ks[tt * MAXD + i] = kv;
+                gs[tt * MAXD + i] = gv;
                 sq = fmaf(qv, qv, sq);
                 sk = fmaf(kv, kv, sk);
-                const float l = decay_logit[tok * ((size_t)n_heads * dim) + (size_t)h * dim + i] + dt_bias[(size_t)h * dim + i];
-                gs[tt * dim + i] = expf(-rt * softplus_f(l));
             }
             sq = warp_sum(sq);
             sk = warp_sum(sk);
             const float iq = rsqrtf(sq + 1e-6f) * q_scale, ik = rsqrtf(sk + 1e-6f);
-            for (int i = lane; i < dim; i += 32) {       // a lane rescales what it wrote itself
-                qs[tt * dim + i] *= iq;
-                ks[tt * dim + i] *= ik;
+            for (int i = lane; i < MAXD; i += 32) {      // a lane rescales what it wrote itself
+                qs[tt * MAXD + i] *= iq;
+                ks[tt * MAXD + i] *= ik;
             }
             if (lane == 0) bs[tt] = 1.0f / (1.0f + expf(-to_f32(beta_logit[tok * beta_stride + h])));
         }
@@ -99,43 +108,46 @@ delta_rule_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T
         }
         __syncthreads();
         for (int tt = 0; tt < nt; tt++) {            // (all lanes take part in the sums over a column's four lanes)
-            const size_t tok = (size_t)(tok0 + t0 + tt);
-            const float vv = vs[tt * DR_COLS + (threadIdx.x >> 2)];
-            const float* kr = ks + tt * dim;
-            const float* qr = qs + tt * dim;
-            const float* gr = gs + tt * dim;
-            float dot = 0.f;
+            const float4* k4 = reinterpret_cast<const float4*>(ks + tt * MAXD) + r;
+            const float4* q4 = reinterpret_cast<const float4*>(qs + tt * MAXD) + r;
+            const float4* g4 = reinterpret_cast<const float4*>(gs + tt * MAXD) + r;
+            float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
+            float4 kk[J];
 #pragma unroll
-            for (int ii = 0; ii < R; ii++) {
-                const int i = r + DR_SPLIT * ii;
-                if (i < dim) {
-                    S[ii] *= gr[i];
-                    dot = fmaf(S[ii], kr[i], dot);
-                }
+            for (int jj = 0; jj < J; jj++) {
+                const float4 gg = g4[4 * jj];
+                kk[jj] = k4[4 * jj];
+                S[jj][0] *= gg.x; S[jj][1] *= gg.y; S[jj][2] *= gg.z; S[jj][3] *= gg.w;
+                d0 = fmaf(S[jj][0], kk[jj].x, d0); d1 = fmaf(S[jj][1], kk[jj].y, d1);
+                d2 = fmaf(S[jj][2], kk[jj].z, d2); d3 = fmaf(S[jj][3], kk[jj].w, d3);
             }
+            float dot = (d0 + d1) + (d2 + d3);
             dot += __shfl_xor_sync(0xffffffffu, dot, 1);
             dot += __shfl_xor_sync(0xffffffffu, dot, 2);
-            const float e = bs[tt] * (vv - dot);
-            float acc = 0.f;
+            const float e = bs[tt] * (vs[tt * DR_COLS + (threadIdx.x >> 2)] - dot);
+            float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
 #pragma unroll
-            for (int ii = 0; ii < R; ii++) {
-                const int i = r + DR_SPLIT * ii;
-                if (i < dim) {
-                    S[ii] = fmaf(kr[i], e, S[ii]);
-                    acc = fmaf(S[ii], qr[i], acc);
-                }
+            for (int jj = 0; jj < J; jj++) {
+                const float4 qq = q4[4 * jj];
+                S[jj][0] = fmaf(kk[jj].x, e, S[jj][0]); S[jj][1] = fmaf(kk[jj].y, e, S[jj][1]);
+                S[jj][2] = fmaf(kk[jj].z, e, S[jj][2]); S[jj][3] = fmaf(kk[jj].w, e, S[jj][3]);
+                a0 = fmaf(S[jj][0], qq.x, a0); a1 = fmaf(S[jj][1], qq.y, a1);
+                a2 = fmaf(S[jj][2], qq.z, a2); a3 = fmaf(S[jj][3], qq.w, a3);
             }
+            float acc = (a0 + a1) + (a2 + a3);
             acc += __shfl_xor_sync(0xffffffffu, acc, 1);
             acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-            if (live && r == 0) o[tok * ((size_t)n_heads * vdim) + (size_t)h * vdim + col] = acc;
+            if (live && r == 0) o[(size_t)(tok0 + t0 + tt) * ((size_t)n_heads * vdim) + (size_t)h * vdim + col] = acc;
         }
     }
     if (live) {
 #pragma unroll
-        for (int ii = 0; ii < R; ii++) {
-            const int i = r + DR_SPLIT * ii;
-            if (i < dim) srow[(size_t)i * vdim + col] = S[ii];
-        }
+        for (int jj = 0; jj < J; jj++)
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                const int i = 16 * jj + 4 * r + e;
+                if (i < dim) srow[(size_t)i * vdim + col] = S[jj][e];
+            }
     }
 }
 
@@ -185,11 +197,11 @@ extern "C" int ti_delta_rule_scan(const void* q, const void* k, const void* v, l
                "delta_rule_scan: bad sizes");
     TI_REQUIRE(dim <= 128, "delta_rule: heads of %d query/key elements are not supported (up to 128)", dim);
     const int threads = DR_SPLIT * DR_COLS, groups = (vdim + DR_COLS - 1) / DR_COLS;
-    const size_t smem = (size_t)(3 * DR_TOK * dim + DR_TOK + DR_TOK * DR_COLS) * sizeof(float);
     return ti_dispatch_dtype(dtype, [&](auto t) -> int {
         using T = decltype(t);
         return dispatch_dim(dim, [&](auto md) -> int {
             constexpr int MAXD = decltype(md)::value;
+            constexpr size_t smem = (size_t)(3 * DR_TOK * MAXD + DR_TOK + DR_TOK * DR_COLS) * sizeof(float);
             TI_CUDA(ti_launch(delta_rule_scan_kernel<T, MAXD>, dim3(n_heads * groups, n_seq), dim3(threads), smem, stream,
                               (const T*)q, (const T*)k, (const T*)v, q_stride, k_stride, v_stride, decay_logit, dt_bias, rate,
                               (const T*)beta_logit, beta_stride, o, state, slot_stride, cu_new, seq_slot, n_heads, qk_heads, dim,

@@ -40,11 +40,14 @@ def prepare(qkv: torch.Tensor, bias: Optional[torch.Tensor], q_w: Optional[torch
           _code(qkv, "attention_bias"), _stream())
 
 
-def decode_splits(n_seq: int, n_heads: int, plan_len: int, sms: int) -> int:
+def decode_splits(n_seq: int, n_heads: int, n_kv_heads: int, plan_len: int, sms: int) -> int:
     """Ranges that a single query's keys are cut into, so that the step has about four blocks per SM but no range
-    shorter than 256 keys: depends only on the batch's padded size and the length the step was planned for."""
-    want = max(1, (4 * sms) // max(1, n_seq * n_heads))
-    return max(1, min(want, (plan_len + 255) // 256, 64))
+    shorter than 128 keys: depends only on the batch's padded size and the length the step was planned for.  (A block
+    takes up to four query heads of a kv head: csrc/attn_bias.cu.)"""
+    group = n_heads // n_kv_heads
+    per_block = 4 if group % 4 == 0 else 2 if group % 2 == 0 else 1
+    want = max(1, (4 * sms) // max(1, n_seq * n_heads // per_block))
+    return max(1, min(want, (plan_len + 127) // 128, 64))
 
 
 tensor_cores = True          # tests clear this to run prompts and pieces on the CUDA-core kernel whatever their sizes
@@ -69,7 +72,7 @@ def attend(q: torch.Tensor, vdim: int, mem, scale: float, cap: float, dist_bias:
     out = torch.zeros((M, H * vdim), dtype=q.dtype, device=q.device)
     code = _code(q, "attention_bias")
     if batch.mode == "extend":
-        splits = decode_splits(M, H, batch.plan_len, sm_count(q.device))
+        splits = decode_splits(M, H, mem.n_kv_heads, batch.plan_len, sm_count(q.device))
         part_o = part_ml = None
         if splits > 1:
             part_o = torch.empty((M, H, splits, vdim), dtype=torch.float32, device=q.device)

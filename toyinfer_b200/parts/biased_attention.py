@@ -23,6 +23,7 @@ import torch
 
 from .. import kernels as K
 from ..kernels import attention_bias as KA
+from ..kernels.gemm import sm_count
 from ..tracing import ranged
 from .base import BuildContext, KVRequest, Mixer, ParamSpec, register_part
 
@@ -104,7 +105,7 @@ class BiasedAttention(Mixer):
         return KVRequest(self.n_kv, self.dim, 0, True, self.vdim if self.vdim != self.dim else 0)
 
     def launch_plan(self, n_seq: int, plan_len: int, dtype, device, n_live=None):
-        return ("biased", KA.decode_splits(n_seq, self.n_heads, plan_len, K.gemm.sm_count(device)))
+        return ("biased", KA.decode_splits(n_seq, self.n_heads, self.n_kv, plan_len, sm_count(device)))
 
     def forward(self, x, batch, mem, shared) -> torch.Tensor:
         if mem is None or not hasattr(mem, "k_pages"):
