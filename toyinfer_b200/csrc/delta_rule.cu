@@ -72,41 +72,62 @@ delta_rule_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T
             const int i = 16 * jj + 4 * r + e;
             S[jj][e] = (live && i < dim) ? srow[(size_t)i * vdim + col] : 0.f;
         }
+    // A run's operands are fetched into registers while the run before it is worked off: a warp brings TPW tokens'
+    // q, k and decay logits (EPL elements a lane each), a thread VPT of the run's values.
+    constexpr int TPW = DR_TOK / DR_SPLIT, EPL = MAXD / 32, VPT = DR_TOK * DR_COLS / (DR_SPLIT * DR_COLS);
+    float rq[TPW][EPL], rk[TPW][EPL], rl[TPW][EPL], rb[TPW], rv[VPT], dtb[EPL];
+#pragma unroll
+    for (int e = 0; e < EPL; e++) dtb[e] = lane + 32 * e < dim ? dt_bias[(size_t)h * dim + lane + 32 * e] : 0.f;
+    auto fetch = [&](int t0) {
+        const int nt = min(DR_TOK, n - t0);
+#pragma unroll
+        for (int j = 0; j < TPW; j++) {
+            const int tt = warp + n_warps * j;
+            const size_t tok = (size_t)(tok0 + t0 + min(tt, nt - 1));
+#pragma unroll
+            for (int e = 0; e < EPL; e++) {
+                const int i = lane + 32 * e;
+                const bool ok = i < dim && tt < nt;
+                rq[j][e] = ok ? to_f32(q[tok * q_stride + (size_t)hq * dim + i]) : 0.f;
+                rk[j][e] = ok ? to_f32(k[tok * k_stride + (size_t)hq * dim + i]) : 0.f;
+                rl[j][e] = ok ? decay_logit[tok * ((size_t)n_heads * dim) + (size_t)h * dim + i] : 0.f;
+            }
+            rb[j] = to_f32(beta_logit[tok * beta_stride + h]);
+        }
+#pragma unroll
+        for (int m = 0; m < VPT; m++) {
+            const int idx = threadIdx.x + DR_SPLIT * DR_COLS * m, tt = idx / DR_COLS, c = g * DR_COLS + (idx - tt * DR_COLS);
+            rv[m] = (tt < nt && c < vdim) ? to_f32(v[(size_t)(tok0 + t0 + tt) * v_stride + (size_t)h * vdim + c]) : 0.f;
+        }
+    };
+    fetch(0);
     for (int t0 = 0; t0 < n; t0 += DR_TOK) {
         const int nt = min(DR_TOK, n - t0);
-        __syncthreads();
-        for (int tt = warp; tt < nt; tt += n_warps) {
-            const size_t tok = (size_t)(tok0 + t0 + tt);
+        __syncthreads();             // the run before is worked off
+#pragma unroll
+        for (int j = 0; j < TPW; j++) {
+            const int tt = warp + n_warps * j;
             float sq = 0.f, sk = 0.f;
-            for (int i = lane; i < MAXD; i += 32) {
-                float qv = 0.f, kv = 0.f, gv = 0.f;
-                if (i < dim) {
-                    qv = to_f32(q[tok * q_stride + (size_t)hq * dim + i]);
-                    kv = to_f32(k[tok * k_stride + (size_t)hq * dim + i]);
-                    const float l = decay_logit[tok * ((size_t)n_heads * dim) + (size_t)h * dim + i] + dt_bias[(size_t)h * dim + i];
-                    gv = expf(-rt * softplus_f(l));
-                }
-                qs[tt * MAXD + i] = qv;
-                ks[tt * MAXD + i] = kv;
-                gs[tt * MAXD + i] = gv;
-                sq = fmaf(qv, qv, sq);
-                sk = fmaf(kv, kv, sk);
-            }
+#pragma unroll
+            for (int e = 0; e < EPL; e++) { sq = fmaf(rq[j][e], rq[j][e], sq); sk = fmaf(rk[j][e], rk[j][e], sk); }
             sq = warp_sum(sq);
             sk = warp_sum(sk);
             const float iq = rsqrtf(sq + 1e-6f) * q_scale, ik = rsqrtf(sk + 1e-6f);
-            for (int i = lane; i < MAXD; i += 32) {      // a lane rescales what it wrote itself
-                qs[tt * MAXD + i] *= iq;
-                ks[tt * MAXD + i] *= ik;
+            if (tt < nt) {
+#pragma unroll
+                for (int e = 0; e < EPL; e++) {
+                    const int i = lane + 32 * e;
+                    qs[tt * MAXD + i] = rq[j][e] * iq;
+                    ks[tt * MAXD + i] = rk[j][e] * ik;
+                    gs[tt * MAXD + i] = i < dim ? expf(-rt * softplus_f(rl[j][e] + dtb[e])) : 0.f;
+                }
+                if (lane == 0) bs[tt] = 1.0f / (1.0f + expf(-rb[j]));
             }
-            if (lane == 0) bs[tt] = 1.0f / (1.0f + expf(-to_f32(beta_logit[tok * beta_stride + h])));
         }
-        // the run's values too, all loads on their way at once: the recurrence below would wait for each in turn
-        for (int idx = threadIdx.x; idx < nt * DR_COLS; idx += blockDim.x) {
-            const int tt = idx / DR_COLS, c = g * DR_COLS + (idx - tt * DR_COLS);
-            vs[idx] = c < vdim ? to_f32(v[(size_t)(tok0 + t0 + tt) * v_stride + (size_t)h * vdim + c]) : 0.f;
-        }
+#pragma unroll
+        for (int m = 0; m < VPT; m++) vs[threadIdx.x + DR_SPLIT * DR_COLS * m] = rv[m];
         __syncthreads();
+        if (t0 + DR_TOK < n) fetch(t0 + DR_TOK);          // on its way while this run is worked off
         for (int tt = 0; tt < nt; tt++) {            // (all lanes take part in the sums over a column's four lanes)
             const float4* k4 = reinterpret_cast<const float4*>(ks + tt * MAXD) + r;
             const float4* q4 = reinterpret_cast<const float4*>(qs + tt * MAXD) + r;
