@@ -105,10 +105,12 @@ def delta_rule(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay_logit: t
     _vec(rate, H, "delta_rule: the rates")
     base, stride = _state_part(state, state_offset, H * dim * vdim, "delta_rule")
     o = torch.zeros((M, H * vdim), dtype=torch.float32, device=q.device)
-    _call(_fn("ti_delta_rule_scan", [P, P, P, L, L, L, P, P, P, P, L, P, P, L, P, P, I, I, I, I, I, I, P]),
+    # unit queries and keys, decays and betas of all tokens, made by a kernel of their own before the recurrence
+    scratch = torch.empty(M * (2 * G * dim + H * dim + H), dtype=torch.float32, device=q.device)
+    _call(_fn("ti_delta_rule_scan", [P, P, P, L, L, L, P, P, P, P, L, P, P, L, P, P, P, I, I, I, I, I, I, I, P]),
           _ptr(q), _ptr(k), _ptr(v), q.stride(0), k.stride(0), v.stride(0), _ptr(decay_logit), _ptr(dt_bias), _ptr(rate),
-          _ptr(beta_logit), beta_logit.stride(0), _ptr(o), base, stride, _ptr(batch.cu_new), _ptr(batch.seq_slot), batch.n_seq,
-          H, G, dim, vdim, _code(q, "delta_rule"), _stream())
+          _ptr(beta_logit), beta_logit.stride(0), _ptr(o), base, stride, _ptr(scratch), _ptr(batch.cu_new), _ptr(batch.seq_slot),
+          batch.n_seq, M, H, G, dim, vdim, _code(q, "delta_rule"), _stream(), launches=2)
     return o
 
 
